@@ -1,0 +1,126 @@
+/*
+ * tcec.h - C ABI of the B200 (sm_100a) error-corrected SGEMM emulation.
+ *
+ * FP32 GEMM computed on tensor cores: every input is split into a low-precision
+ * head and a scaled residual, three tensor-core products are formed, and the
+ * correction term is folded back in FP32 (algorithm of wmma_extension's
+ * mtk::wmma::tcec, include/wmma_extension/tcec/tcec.hpp).
+ *
+ * All matrix pointers are DEVICE pointers owned by the caller.  Calls are
+ * asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default
+ * stream) and return an integer status, never throw and never exit.  The
+ * library owns only its cached workspace and a device status word, created on
+ * first use per device and released by tcec_destroy().
+ *
+ * The reference has no host API: its closest counterpart is the launch glue of
+ * its batched example, launch_bgemm() (test/tcec/batch_gemm.cu:433-443) and the
+ * cublasSgemmBatched call it is benchmarked against (test/tcec/batch_gemm.cu:619-621).
+ * Argument order follows those.
+ */
+#ifndef TCEC_H_
+#define TCEC_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define TCEC_OK 0
+#define TCEC_ERR_INVALID_ARGUMENT 1
+#define TCEC_ERR_UNSUPPORTED 2
+#define TCEC_ERR_CUDA 3
+#define TCEC_ERR_TIMEOUT 4 /* a bounded device-side wait ran out */
+#define TCEC_ERR_ALLOC 5
+
+/* storage order of a matrix: element (i,j) at i*ld + j (row) or i + j*ld (col) */
+#define TCEC_ROW_MAJOR 0
+#define TCEC_COL_MAJOR 1
+
+/*
+ * Policies: input type of the tensor-core products x error correction.
+ * Mirrors the reference's fragment type T (half / nvcuda::wmma::precision::tf32)
+ * and its with_ec / without_ec tags (include/wmma_extension/tcec/detail/policy.hpp:12-20).
+ */
+#define TCEC_POLICY_FP16_EC 0
+#define TCEC_POLICY_TF32_EC 1
+#define TCEC_POLICY_FP16_NO_EC 2
+#define TCEC_POLICY_TF32_NO_EC 3
+
+/*
+ * C = alpha * A(m x k) * B(k x n) + beta * C(m x n).
+ * Replaces launch_bgemm() with batch 1 (test/tcec/batch_gemm.cu:433-443); the
+ * kernel it stands for is bgemm_kernel (test/tcec/batch_gemm.cu:261-386), whose
+ * fixed layout (A row-major, B col-major, C col-major) is one of the eight
+ * layout combinations accepted here.  beta == 0 never reads C, as in the
+ * reference epilogue (test/tcec/batch_gemm.cu:124-158).
+ */
+int tcec_sgemm(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+               const float* a, long long lda, const float* b, long long ldb, float beta, float* c,
+               long long ldc, int policy, void* stream);
+
+/*
+ * Pointer-array batch: a_array/b_array/c_array are DEVICE arrays of `batch`
+ * device pointers, one matrix each, all of the same shape and leading
+ * dimensions.  Replaces launch_bgemm() (test/tcec/batch_gemm.cu:433-443), same
+ * argument meaning as cublasSgemmBatched (test/tcec/batch_gemm.cu:619-621).
+ */
+int tcec_sgemm_batched(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+                       const float* const* a_array, long long lda, const float* const* b_array,
+                       long long ldb, float beta, float* const* c_array, long long ldc, int batch,
+                       int policy, void* stream);
+
+/*
+ * Strided batch: matrix i of A starts at a + i*stride_a (elements), likewise B
+ * and C.  Convenience form of the pointer-array batch above for contiguous
+ * batches (the reference allocates one buffer per matrix, test/tcec/batch_gemm.cu:469-533).
+ */
+int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, int n, int k,
+                               float alpha, const float* a, long long lda, long long stride_a,
+                               const float* b, long long ldb, long long stride_b, float beta,
+                               float* c, long long ldc, long long stride_c, int batch, int policy,
+                               void* stream);
+
+/*
+ * Element-wise split, exposed so the split can be checked bit for bit:
+ *   hi[i] = cast<T>(in[i]);  lo[i] = cast<T>((in[i] - hi[i]) * s)
+ * returned widened to float (lo still carries the scale s = 2^11 for fp16, 1 for
+ * tf32).  Restates load_matrix_sync's per-element arithmetic
+ * (include/wmma_extension/tcec/tcec.hpp:219-223; scale.hpp:8-13).  `lo` may be
+ * NULL.  Only the input type of `policy` matters.
+ */
+int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, void* stream);
+
+/*
+ * Options (process-wide):
+ *   "promote_k"  K extent accumulated inside the tensor-core accumulator before
+ *                it is added to the FP32 running sum with a round-to-nearest add
+ *                (default 128; 0 = only at the end, the reference's mma_rz_sync
+ *                behaviour, include/wmma_extension/tcec/tcec.hpp:773-831; the
+ *                reference's mma_rn_sync uses 16 or 8, :640-706).
+ *   "tile_n"     0 = automatic, 128 or 256.
+ */
+int tcec_set_option(const char* name, int value);
+int tcec_get_option(const char* name, int* value);
+
+/*
+ * Synchronises the current device and returns TCEC_ERR_TIMEOUT if any kernel
+ * of this library gave up a bounded wait since the last call, else TCEC_OK.
+ * `detail`, when not NULL, receives the raw device status word.
+ */
+int tcec_device_status(int* detail);
+
+/* Bytes of library-owned workspace a call of this shape will use (0 on error). */
+size_t tcec_workspace_bytes(int m, int n, int k, int batch, int policy);
+
+/* Frees every cached workspace on every device. */
+int tcec_destroy(void);
+
+const char* tcec_status_string(int status);
+const char* tcec_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCEC_H_ */

@@ -1,0 +1,408 @@
+// Host side of the C ABI declared in include/tcec.h: argument checks, the
+// library-owned workspace, kernel selection and launches.  No CPU compute path
+// exists here: every entry point either launches sm_100a kernels or fails.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "../../include/tcec.h"
+#include "tcec_gemm_panels.cuh"
+#include "tcec_panels.cuh"
+
+using namespace tcec_sm100;
+
+namespace {
+
+struct Workspace {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+struct DeviceState {
+  int* status = nullptr;
+  int sm_count = 0;
+  bool attrs_done = false;
+  std::map<cudaStream_t, Workspace> ws;
+};
+
+std::mutex g_mu;
+std::map<int, DeviceState> g_dev;
+int g_promote_k = 128;
+int g_tile_n = 0;
+
+#define TCEC_CUDA(call)                        \
+  do {                                         \
+    cudaError_t e_ = (call);                   \
+    if (e_ != cudaSuccess) return TCEC_ERR_CUDA; \
+  } while (0)
+
+template <int BN, bool T, bool E>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(tcec_gemm_panels_kernel<BN, T, E>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmPanelCfg<BN, T, E>::SMEM_BYTES);
+}
+
+int get_device_state(DeviceState** out) {
+  int dev = 0;
+  TCEC_CUDA(cudaGetDevice(&dev));
+  DeviceState& st = g_dev[dev];
+  if (!st.attrs_done) {
+    int major = 0;
+    TCEC_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return TCEC_ERR_UNSUPPORTED;  // sm_100a only
+    TCEC_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    TCEC_CUDA((set_smem_attr<128, false, false>()));
+    TCEC_CUDA((set_smem_attr<128, false, true>()));
+    TCEC_CUDA((set_smem_attr<128, true, false>()));
+    TCEC_CUDA((set_smem_attr<128, true, true>()));
+    TCEC_CUDA((set_smem_attr<256, false, false>()));
+    TCEC_CUDA((set_smem_attr<256, false, true>()));
+    TCEC_CUDA((set_smem_attr<256, true, false>()));
+    TCEC_CUDA((set_smem_attr<256, true, true>()));
+    if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return TCEC_ERR_ALLOC;
+    TCEC_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+    st.attrs_done = true;
+  }
+  *out = &st;
+  return TCEC_OK;
+}
+
+int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out) {
+  Workspace& w = st->ws[stream];
+  if (w.bytes < bytes) {
+    if (w.ptr) {
+      // Work queued on this stream may still read the old buffer.
+      TCEC_CUDA(cudaStreamSynchronize(stream));
+      cudaFree(w.ptr);
+      w.ptr = nullptr;
+      w.bytes = 0;
+    }
+    if (cudaMalloc(&w.ptr, bytes) != cudaSuccess) {
+      w.ptr = nullptr;
+      return TCEC_ERR_ALLOC;
+    }
+    w.bytes = bytes;
+  }
+  *out = w.ptr;
+  return TCEC_OK;
+}
+
+struct Shape {
+  int tile_n, tiles_m, tiles_n, nkb, kop, np;
+  size_t a_bytes, b_bytes;  // per matrix
+};
+Shape plan(int m, int n, int k, int policy) {
+  Shape s;
+  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
+  const bool ec = (policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC);
+  s.kop = tf32 ? 16 : 32;
+  s.np = ec ? 2 : 1;
+  s.tile_n = g_tile_n ? g_tile_n : (n > 128 ? 256 : 128);
+  s.tiles_m = (m + 127) / 128;
+  s.tiles_n = (n + s.tile_n - 1) / s.tile_n;
+  s.nkb = (k + s.kop - 1) / s.kop;
+  s.a_bytes = static_cast<size_t>(s.tiles_m) * s.nkb * s.np * kPanelBytes;
+  s.b_bytes = static_cast<size_t>(s.tiles_n) * (s.tile_n / 128) * s.nkb * s.np * kPanelBytes;
+  return s;
+}
+
+__global__ void scale_c_kernel(float* c, float* const* c_array, long long ldc, long long stride,
+                               int rows, int cols, int col_major, float beta) {
+  float* base = c_array ? c_array[blockIdx.z] : c + blockIdx.z * stride;
+  const int inner = col_major ? rows : cols, outer = col_major ? cols : rows;
+  for (int o = blockIdx.y; o < outer; o += gridDim.y)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inner; i += gridDim.x * blockDim.x) {
+      float* p = base + static_cast<long long>(o) * ldc + i;
+      *p = (beta == 0.f) ? 0.f : beta * *p;
+    }
+}
+
+template <bool T>
+__global__ void split_flat_kernel(const float* __restrict__ in, float* hi, float* lo, size_t n) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float v = in[i];
+    float h, l;
+    if constexpr (T) {
+      h = tf32_rna(v);
+      l = tf32_rna(v - h);
+    } else {
+      const __half hh = __float2half_rn(v);
+      h = __half2float(hh);
+      l = __half2float(__float2half_rn((v - h) * 2048.0f));
+    }
+    hi[i] = h;
+    if (lo) lo[i] = l;
+  }
+}
+
+template <bool T, bool E>
+void launch_split(const SplitParams& sp, int batch, cudaStream_t stream) {
+  dim3 grid(sp.nkb, sp.row_blocks, batch);
+  tcec_split_panels_kernel<T, E><<<grid, 256, 0, stream>>>(sp);
+}
+
+template <int BN, bool T, bool E>
+void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
+  using Cfg = GemmPanelCfg<BN, T, E>;
+  const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * gp.batch;
+  const int grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
+  tcec_gemm_panels_kernel<BN, T, E><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(gp);
+}
+
+bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
+
+int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const float* a,
+              const float* const* a_array, long long lda, long long stride_a, const float* b,
+              const float* const* b_array, long long ldb, long long stride_b, float beta, float* c,
+              float* const* c_array, long long ldc, long long stride_c, int batch, int policy,
+              void* stream_v) {
+  if (bad_layout(la) || bad_layout(lb) || bad_layout(lc)) return TCEC_ERR_INVALID_ARGUMENT;
+  if (m < 0 || n < 0 || k < 0 || batch < 0) return TCEC_ERR_INVALID_ARGUMENT;
+  if (policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0 || batch == 0) return TCEC_OK;
+  if (!c && !c_array) return TCEC_ERR_INVALID_ARGUMENT;
+  if (ldc < (lc == TCEC_ROW_MAJOR ? n : m)) return TCEC_ERR_INVALID_ARGUMENT;
+  if (k > 0) {
+    if ((!a && !a_array) || (!b && !b_array)) return TCEC_ERR_INVALID_ARGUMENT;
+    if (lda < (la == TCEC_ROW_MAJOR ? k : m)) return TCEC_ERR_INVALID_ARGUMENT;
+    if (ldb < (lb == TCEC_ROW_MAJOR ? n : k)) return TCEC_ERR_INVALID_ARGUMENT;
+  }
+  if (batch > 65535) return TCEC_ERR_UNSUPPORTED;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != TCEC_OK) return rc;
+
+  if (k == 0 || alpha == 0.f) {
+    if (beta == 1.f) return TCEC_OK;
+    const int inner = lc == TCEC_COL_MAJOR ? m : n, outer = lc == TCEC_COL_MAJOR ? n : m;
+    dim3 grid((inner + 255) / 256, outer < 65535 ? outer : 65535, batch);
+    scale_c_kernel<<<grid, 256, 0, stream>>>(c, c_array, ldc, stride_c, m, n, lc == TCEC_COL_MAJOR,
+                                             beta);
+    TCEC_CUDA(cudaGetLastError());
+    return TCEC_OK;
+  }
+
+  const Shape s = plan(m, n, k, policy);
+  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
+  const bool ec = (policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC);
+  void* ws = nullptr;
+  rc = get_workspace(st, stream, (s.a_bytes + s.b_bytes) * batch, &ws);
+  if (rc != TCEC_OK) return rc;
+  uint8_t* panels_a = static_cast<uint8_t*>(ws);
+  uint8_t* panels_b = panels_a + s.a_bytes * batch;
+
+  SplitParams spa{};
+  spa.src = a;
+  spa.src_array = a_array;
+  spa.ld = lda;
+  spa.batch_stride = stride_a;
+  spa.rows = m;
+  spa.k = k;
+  spa.k_contiguous = (la == TCEC_ROW_MAJOR);
+  spa.row_blocks = s.tiles_m;
+  spa.nkb = s.nkb;
+  spa.panels = panels_a;
+  spa.panels_batch_stride = static_cast<long long>(s.a_bytes);
+  spa.mul = 1.0f;
+  SplitParams spb{};
+  spb.src = b;
+  spb.src_array = b_array;
+  spb.ld = ldb;
+  spb.batch_stride = stride_b;
+  spb.rows = n;
+  spb.k = k;
+  spb.k_contiguous = (lb == TCEC_COL_MAJOR);
+  spb.row_blocks = s.tiles_n * (s.tile_n / 128);
+  spb.nkb = s.nkb;
+  spb.panels = panels_b;
+  spb.panels_batch_stride = static_cast<long long>(s.b_bytes);
+  spb.mul = 1.0f;
+
+  GemmPanelParams gp{};
+  gp.M = m;
+  gp.N = n;
+  gp.K = k;
+  gp.batch = batch;
+  gp.nkb = s.nkb;
+  gp.tiles_m = s.tiles_m;
+  gp.tiles_n = s.tiles_n;
+  gp.promo = g_promote_k > 0 ? (g_promote_k + s.kop - 1) / s.kop : 0;
+  gp.alpha = alpha;
+  gp.beta = beta;
+  gp.panels_a = panels_a;
+  gp.panels_b = panels_b;
+  gp.panels_a_batch_stride = static_cast<long long>(s.a_bytes);
+  gp.panels_b_batch_stride = static_cast<long long>(s.b_bytes);
+  gp.c = c;
+  gp.c_array = c_array;
+  gp.ldc = ldc;
+  gp.c_batch_stride = stride_c;
+  gp.c_col_major = (lc == TCEC_COL_MAJOR);
+  gp.status = st->status;
+
+#define TCEC_DISPATCH(T, E)                                      \
+  do {                                                           \
+    launch_split<T, E>(spa, batch, stream);                      \
+    launch_split<T, E>(spb, batch, stream);                      \
+    if (s.tile_n == 256)                                         \
+      launch_gemm<256, T, E>(gp, st->sm_count, stream);          \
+    else                                                         \
+      launch_gemm<128, T, E>(gp, st->sm_count, stream);          \
+  } while (0)
+  if (tf32 && ec)
+    TCEC_DISPATCH(true, true);
+  else if (tf32)
+    TCEC_DISPATCH(true, false);
+  else if (ec)
+    TCEC_DISPATCH(false, true);
+  else
+    TCEC_DISPATCH(false, false);
+#undef TCEC_DISPATCH
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tcec_sgemm(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+               const float* a, long long lda, const float* b, long long ldb, float beta, float* c,
+               long long ldc, int policy, void* stream) {
+  return gemm_impl(layout_a, layout_b, layout_c, m, n, k, alpha, a, nullptr, lda, 0, b, nullptr,
+                   ldb, 0, beta, c, nullptr, ldc, 0, 1, policy, stream);
+}
+
+int tcec_sgemm_batched(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+                       const float* const* a_array, long long lda, const float* const* b_array,
+                       long long ldb, float beta, float* const* c_array, long long ldc, int batch,
+                       int policy, void* stream) {
+  return gemm_impl(layout_a, layout_b, layout_c, m, n, k, alpha, nullptr, a_array, lda, 0, nullptr,
+                   b_array, ldb, 0, beta, nullptr, c_array, ldc, 0, batch, policy, stream);
+}
+
+int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, int n, int k,
+                               float alpha, const float* a, long long lda, long long stride_a,
+                               const float* b, long long ldb, long long stride_b, float beta,
+                               float* c, long long ldc, long long stride_c, int batch, int policy,
+                               void* stream) {
+  return gemm_impl(layout_a, layout_b, layout_c, m, n, k, alpha, a, nullptr, lda, stride_a, b,
+                   nullptr, ldb, stride_b, beta, c, nullptr, ldc, stride_c, batch, policy, stream);
+}
+
+int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, void* stream) {
+  if (policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
+  if (count == 0) return TCEC_OK;
+  if (!in || !hi) return TCEC_ERR_INVALID_ARGUMENT;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* st = nullptr;
+    const int rc = get_device_state(&st);
+    if (rc != TCEC_OK) return rc;
+  }
+  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
+  const size_t want = (count + 255) / 256;
+  const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  if (tf32)
+    split_flat_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(in, hi, lo, count);
+  else
+    split_flat_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(in, hi, lo, count);
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
+int tcec_set_option(const char* name, int value) {
+  if (!name) return TCEC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!strcmp(name, "promote_k")) {
+    if (value < 0) return TCEC_ERR_INVALID_ARGUMENT;
+    g_promote_k = value;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "tile_n")) {
+    if (value != 0 && value != 128 && value != 256) return TCEC_ERR_INVALID_ARGUMENT;
+    g_tile_n = value;
+    return TCEC_OK;
+  }
+  return TCEC_ERR_INVALID_ARGUMENT;
+}
+
+int tcec_get_option(const char* name, int* value) {
+  if (!name || !value) return TCEC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!strcmp(name, "promote_k")) {
+    *value = g_promote_k;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "tile_n")) {
+    *value = g_tile_n;
+    return TCEC_OK;
+  }
+  return TCEC_ERR_INVALID_ARGUMENT;
+}
+
+int tcec_device_status(int* detail) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = nullptr;
+  const int rc = get_device_state(&st);
+  if (rc != TCEC_OK) return rc;
+  TCEC_CUDA(cudaDeviceSynchronize());
+  int word = 0;
+  TCEC_CUDA(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (detail) *detail = word;
+  if (word != 0) {
+    TCEC_CUDA(cudaMemset(st->status, 0, sizeof(int)));
+    return TCEC_ERR_TIMEOUT;
+  }
+  return TCEC_OK;
+}
+
+size_t tcec_workspace_bytes(int m, int n, int k, int batch, int policy) {
+  if (m <= 0 || n <= 0 || k <= 0 || batch <= 0 || policy < 0 || policy > 3) return 0;
+  std::lock_guard<std::mutex> lock(g_mu);
+  const Shape s = plan(m, n, k, policy);
+  return (s.a_bytes + s.b_bytes) * batch;
+}
+
+int tcec_destroy(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (auto& kv : g_dev) {
+    if (cudaSetDevice(kv.first) != cudaSuccess) continue;
+    cudaDeviceSynchronize();
+    for (auto& w : kv.second.ws)
+      if (w.second.ptr) cudaFree(w.second.ptr);
+    kv.second.ws.clear();
+    if (kv.second.status) cudaFree(kv.second.status);
+    kv.second.status = nullptr;
+    kv.second.attrs_done = false;
+  }
+  g_dev.clear();
+  cudaSetDevice(cur);
+  return TCEC_OK;
+}
+
+const char* tcec_status_string(int status) {
+  switch (status) {
+    case TCEC_OK: return "ok";
+    case TCEC_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case TCEC_ERR_UNSUPPORTED: return "unsupported (needs an sm_100a device)";
+    case TCEC_ERR_CUDA: return "CUDA runtime error";
+    case TCEC_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case TCEC_ERR_ALLOC: return "workspace allocation failed";
+    default: return "unknown status";
+  }
+}
+
+const char* tcec_version(void) { return "tcec-b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,347 @@
+// Three-product error-corrected GEMM on tcgen05 over pre-split operand panels.
+//
+// Restates the reference accumulation (include/wmma_extension/tcec/tcec.hpp:640-706,
+// fold at :332-336) at tile scale:
+//   main  : A_hi*B_hi accumulates in TMEM for `promo` k-blocks, then is added to
+//           an FP32 register accumulator with a round-to-nearest FADD (the
+//           reference does this every 16 of K because the tensor-core
+//           accumulator truncates; the interval here is a launch parameter);
+//   corr  : A_lo*B_hi + A_hi*B_lo accumulates in a second TMEM region for the
+//           whole K loop, as in the reference;
+//   store : C = alpha * (main + corr / 2^11) + beta * C   (tf32: corr / 1).
+// Without error correction only the main product exists.
+//
+// One persistent CTA per SM.  Roles by warp:
+//   warp 0      producer  - linear bulk copies of operand panels into a ring
+//   warp 1      MMA       - one elected thread issues tcgen05.mma, owns TMEM
+//   warps 4..   epilogue  - tcgen05.ld, RN promotion, fold, alpha/beta, stores
+// All hand-offs are mbarriers; every wait is bounded and raises `status`.
+#pragma once
+#include "sm100_ptx.cuh"
+#include "tcec_panels.cuh"
+
+namespace tcec_sm100 {
+
+struct GemmPanelParams {
+  int M, N, K;
+  int batch;
+  int nkb;                 // k blocks (panels along K)
+  int tiles_m, tiles_n;    // tiles per matrix
+  int promo;               // k blocks per RN promotion; 0 = promote once, at the end
+  float alpha, beta;
+  const uint8_t* panels_a; // [batch][tiles_m][nkb][hi,lo]
+  const uint8_t* panels_b; // [batch][n row blocks of 128][nkb][hi,lo]
+  long long panels_a_batch_stride, panels_b_batch_stride;  // bytes
+  float* c;                // strided base (used when c_array == nullptr)
+  float* const* c_array;
+  long long ldc, c_batch_stride;
+  int c_col_major;
+  int* status;             // device word; non-zero after a wait ran out
+};
+
+enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3 };
+
+template <int BN, bool kTf32, bool kEc>
+struct GemmPanelCfg {
+  static constexpr int BM = 128;
+  static constexpr int NB = BN / 128;                  // 128-row B panels per tile
+  static constexpr int NP = kEc ? 2 : 1;               // hi (+ lo)
+  static constexpr int A_BYTES = kPanelBytes * NP;
+  static constexpr int B_BYTES = kPanelBytes * NP * NB;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NST_RAW = (208 * 1024) / STAGE_BYTES;
+  static constexpr int NST = NST_RAW > 8 ? 8 : NST_RAW;
+  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + 1024;
+  static constexpr int TMEM_COLS = kEc ? 2 * BN : BN;  // 128, 256 or 512: powers of two
+  static constexpr int EPI_WARPS = 4 * NB;
+  static constexpr int THREADS = 128 + 32 * EPI_WARPS;
+  static constexpr int GROUP_M = 16;                   // m tiles per raster group
+};
+
+struct TileCoord {
+  int b, mt, nt;
+};
+__device__ __forceinline__ TileCoord decode_tile(int tile, int tiles_m, int tiles_n, int group_m) {
+  const int per = tiles_m * tiles_n;
+  TileCoord t;
+  t.b = tile / per;
+  const int r = tile - t.b * per;
+  const int span = group_m * tiles_n;
+  const int g = r / span;
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, tiles_m - first_m);
+  const int in = r - g * span;
+  t.mt = first_m + in % gsz;
+  t.nt = in / gsz;
+  return t;
+}
+
+template <int BN, bool kTf32, bool kEc>
+__global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
+    tcec_gemm_panels_kernel(const GemmPanelParams p) {
+  using Cfg = GemmPanelCfg<BN, kTf32, kEc>;
+  constexpr int NST = Cfg::NST;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[NST], bar_empty[NST];
+  __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntiles = p.tiles_m * p.tiles_n * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_main_full), 1);
+    mbar_init(smem_u32(&bar_main_free), Cfg::EPI_WARPS);
+    mbar_init(smem_u32(&bar_corr_full), 1);
+    mbar_init(smem_u32(&bar_corr_free), Cfg::EPI_WARPS);
+    mbar_init(smem_u32(&bar_drain), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_main = tmem_base_s;
+  const uint32_t tmem_corr = tmem_base_s + BN;
+  volatile uint32_t* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t armed = 0, armed_parity = 0;  // per stage: a copy was issued, and in which phase
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+        const uint8_t* pa = p.panels_a + tc.b * p.panels_a_batch_stride +
+                            static_cast<size_t>(tc.mt) * p.nkb * Cfg::A_BYTES;
+        const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
+                            static_cast<size_t>(tc.nt) * Cfg::NB * p.nkb * (kPanelBytes * Cfg::NP);
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+          const uint32_t s = it % NST, ph = (it / NST) & 1;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+          armed |= 1u << s;
+          armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+          bulk_load(dst, pa + static_cast<size_t>(kb) * Cfg::A_BYTES, Cfg::A_BYTES, full);
+#pragma unroll
+          for (int h = 0; h < Cfg::NB; ++h) {
+            const uint8_t* src = pb + (static_cast<size_t>(h) * p.nkb + kb) * (kPanelBytes * Cfg::NP);
+            bulk_load(dst + Cfg::A_BYTES + h * kPanelBytes, src, kPanelBytes, full);
+            if constexpr (kEc)
+              bulk_load(dst + Cfg::A_BYTES + (Cfg::NB + h) * kPanelBytes, src + kPanelBytes,
+                        kPanelBytes, full);
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0, kErrProducerWait);
+        // Let this thread's own copies land before the CTA gives up its shared memory.
+        for (uint32_t s = 0; s < static_cast<uint32_t>(NST); ++s)
+          if (armed & (1u << s)) mbar_wait_plain(smem_u32(&bar_full[s]), (armed_parity >> s) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
+      uint32_t it = 0, chunk = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+          const uint32_t s = it % NST, ph = (it / NST) & 1;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+            ok = false;
+            break;
+          }
+          const bool first_in_chunk = p.promo ? (kb % p.promo == 0) : (kb == 0);
+          if (first_in_chunk) {
+            if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp)) {
+              ok = false;
+              break;
+            }
+          }
+          tc_fence_after();
+          const uint32_t a_hi = smem_base + s * Cfg::STAGE_BYTES;
+          const uint32_t a_lo = a_hi + kPanelBytes;
+          const uint32_t b_hi = a_hi + Cfg::A_BYTES;
+          const uint32_t b_lo = b_hi + Cfg::NB * kPanelBytes;
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            umma_ss<kTf32>(tmem_main, umma_desc_kmajor_noswizzle(a_hi + 256 * j, 128, 512),
+                           umma_desc_kmajor_noswizzle(b_hi + 256 * j, 128, 512), idesc,
+                           (first_in_chunk && j == 0) ? 0u : 1u);
+          const bool last_in_chunk = (kb == p.nkb - 1) || (p.promo && ((kb + 1) % p.promo == 0));
+          if (last_in_chunk) {
+            umma_commit(smem_u32(&bar_main_full));
+            ++chunk;
+          }
+          if constexpr (kEc) {
+            if (kb == 0) {
+              if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              umma_ss<kTf32>(tmem_corr, umma_desc_kmajor_noswizzle(a_lo + 256 * j, 128, 512),
+                             umma_desc_kmajor_noswizzle(b_hi + 256 * j, 128, 512), idesc,
+                             (kb == 0 && j == 0) ? 0u : 1u);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              umma_ss<kTf32>(tmem_corr, umma_desc_kmajor_noswizzle(a_hi + 256 * j, 128, 512),
+                             umma_desc_kmajor_noswizzle(b_lo + 256 * j, 128, 512), idesc, 1u);
+          }
+          umma_commit(smem_u32(&bar_empty[s]));
+        }
+        if (!ok) break;
+        if constexpr (kEc) umma_commit(smem_u32(&bar_corr_full));
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0, kErrMmaWait);
+        // Nothing may still be writing TMEM when it is released below.
+        umma_commit(smem_u32(&bar_drain));
+        mbar_wait_plain(smem_u32(&bar_drain), 0);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp - 4;
+    const int q = warp & 3;          // TMEM lane quarter this warp may read
+    const int colbase = (ew >> 2) * 128;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float corr_scale = kTf32 ? 1.0f : (1.0f / 2048.0f);
+    const bool vec_store = !p.c_col_major && (p.ldc % 4 == 0);
+    uint32_t chunk = 0, tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+      const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+      const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
+      float acc[128];
+      for (int c = 0; c < nchunks; ++c, ++chunk) {
+        if (!mbar_wait(smem_u32(&bar_main_full), chunk & 1, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
+          tmem_ld_wait();
+          if (c == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_main_free));
+      }
+      if (!ok) break;
+      if constexpr (kEc) {
+        if (!mbar_wait(smem_u32(&bar_corr_full), tcount & 1, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
+      const int row = tc.mt * 128 + q * 32 + lane;
+      const int col0 = tc.nt * BN + colbase;
+      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        if constexpr (kEc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * corr_scale;
+        }
+        if (row < p.M) {
+          if (!p.c_col_major) {
+            float* crow = cbase + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const int col = col0 + cc * 32 + i;
+              if (vec_ok && col + 3 < p.N) {
+                float4 o;
+                o.x = p.alpha * acc[cc * 32 + i + 0];
+                o.y = p.alpha * acc[cc * 32 + i + 1];
+                o.z = p.alpha * acc[cc * 32 + i + 2];
+                o.w = p.alpha * acc[cc * 32 + i + 3];
+                if (p.beta != 0.f) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + col);
+                  o.x += p.beta * old.x;
+                  o.y += p.beta * old.y;
+                  o.z += p.beta * old.z;
+                  o.w += p.beta * old.w;
+                }
+                *reinterpret_cast<float4*>(crow + col) = o;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (col + e < p.N) {
+                    float o = p.alpha * acc[cc * 32 + i + e];
+                    if (p.beta != 0.f) o += p.beta * crow[col + e];
+                    crow[col + e] = o;
+                  }
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = col0 + cc * 32 + i;
+              if (col < p.N) {
+                float* dst = cbase + static_cast<long long>(col) * p.ldc + row;
+                float o = p.alpha * acc[cc * 32 + i];
+                if (p.beta != 0.f) o += p.beta * *dst;
+                *dst = o;
+              }
+            }
+          }
+        }
+      }
+      if constexpr (kEc) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));
+      }
+    }
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicCAS(p.status, 0, kErrEpilogueWait);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base_s, Cfg::TMEM_COLS);
+}
+
+}  // namespace tcec_sm100

@@ -1,0 +1,230 @@
+"""ctypes binding of the C ABI in ``include/tcec.h`` for torch CUDA tensors.
+
+PyTorch is used for device memory and streams only; all arithmetic happens in
+the sm_100a kernels of ``libtcec_b200.so``.  There is no CPU or eager fallback:
+if the shared library is missing, or no sm_100 device is present, calls raise.
+
+Policy names follow the reference's fragment type and error-correction tags
+(``half`` / ``tf32`` x ``with_ec`` / ``without_ec``,
+include/wmma_extension/tcec/detail/policy.hpp:12-20).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtcec_b200.so")
+
+ROW_MAJOR, COL_MAJOR = 0, 1
+POLICIES = {"fp16_ec": 0, "tf32_ec": 1, "fp16_no_ec": 2, "tf32_no_ec": 3}
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_ALLOC = range(6)
+
+EXPORTED_SYMBOLS = (
+    "tcec_sgemm",
+    "tcec_sgemm_batched",
+    "tcec_sgemm_strided_batched",
+    "tcec_split",
+    "tcec_set_option",
+    "tcec_get_option",
+    "tcec_device_status",
+    "tcec_workspace_bytes",
+    "tcec_destroy",
+    "tcec_status_string",
+    "tcec_version",
+)
+
+_lib = None
+
+
+class TcecError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: status {status} ({status_string(status)})")
+
+
+def load() -> ctypes.CDLL:
+    """Load the in-tree shared library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(there is no fallback path)"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    i, ll, f, p, sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+    lib.tcec_sgemm.argtypes = [i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, p]
+    lib.tcec_sgemm.restype = i
+    lib.tcec_sgemm_batched.argtypes = [i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, i, p]
+    lib.tcec_sgemm_batched.restype = i
+    lib.tcec_sgemm_strided_batched.argtypes = [i, i, i, i, i, i, f, p, ll, ll, p, ll, ll, f, p, ll, ll, i, i, p]
+    lib.tcec_sgemm_strided_batched.restype = i
+    lib.tcec_split.argtypes = [p, p, p, sz, i, p]
+    lib.tcec_split.restype = i
+    lib.tcec_set_option.argtypes = [ctypes.c_char_p, i]
+    lib.tcec_set_option.restype = i
+    lib.tcec_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i)]
+    lib.tcec_get_option.restype = i
+    lib.tcec_device_status.argtypes = [ctypes.POINTER(i)]
+    lib.tcec_device_status.restype = i
+    lib.tcec_workspace_bytes.argtypes = [i, i, i, i, i]
+    lib.tcec_workspace_bytes.restype = sz
+    lib.tcec_destroy.argtypes = []
+    lib.tcec_destroy.restype = i
+    lib.tcec_status_string.argtypes = [i]
+    lib.tcec_status_string.restype = ctypes.c_char_p
+    lib.tcec_version.argtypes = []
+    lib.tcec_version.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+def status_string(status: int) -> str:
+    return load().tcec_status_string(status).decode()
+
+
+def _check(status: int, what: str) -> None:
+    if status != OK:
+        raise TcecError(status, what)
+
+
+def _policy(policy) -> int:
+    if isinstance(policy, str):
+        return POLICIES[policy]
+    return int(policy)
+
+
+def _layout_ld(t: torch.Tensor):
+    """(layout, leading dimension) of a 2-D view, from its strides."""
+    r, c = t.shape[-2], t.shape[-1]
+    s0, s1 = t.stride(-2), t.stride(-1)
+    if s1 == 1 and (s0 >= c or r == 1):
+        return ROW_MAJOR, max(s0, c)
+    if s0 == 1 and (s1 >= r or c == 1):
+        return COL_MAJOR, max(s1, r)
+    raise ValueError("matrix must have unit stride along rows or columns")
+
+
+def _require_cuda_f32(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda or t.dtype != torch.float32:
+            raise ValueError("operands must be float32 CUDA tensors")
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def set_option(name: str, value: int) -> None:
+    _check(load().tcec_set_option(name.encode(), int(value)), f"tcec_set_option({name})")
+
+
+def get_option(name: str) -> int:
+    v = ctypes.c_int(0)
+    _check(load().tcec_get_option(name.encode(), ctypes.byref(v)), f"tcec_get_option({name})")
+    return v.value
+
+
+def device_status() -> int:
+    """Synchronise and raise if a kernel gave up a bounded wait."""
+    detail = ctypes.c_int(0)
+    st = load().tcec_device_status(ctypes.byref(detail))
+    if st != OK:
+        raise TcecError(st, f"device status word {detail.value}")
+    return detail.value
+
+
+def sgemm(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *, alpha: float = 1.0,
+          beta: float = 0.0, policy="fp16_ec") -> torch.Tensor:
+    """C = alpha * A @ B + beta * C for 2-D float32 CUDA tensors (row- or column-major views)."""
+    _require_cuda_f32(a, b)
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2:
+        raise ValueError("inner dimensions differ")
+    if c is None:
+        c = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    _require_cuda_f32(c)
+    la, lda = _layout_ld(a)
+    lb, ldb = _layout_ld(b)
+    lc, ldc = _layout_ld(c)
+    with torch.cuda.device(a.device):
+        st = load().tcec_sgemm(la, lb, lc, m, n, k, alpha, a.data_ptr(), lda, b.data_ptr(), ldb, beta,
+                               c.data_ptr(), ldc, _policy(policy), _stream_ptr())
+    _check(st, "tcec_sgemm")
+    return c
+
+
+def sgemm_strided_batched(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *,
+                          alpha: float = 1.0, beta: float = 0.0, policy="fp16_ec") -> torch.Tensor:
+    """Batched product of 3-D tensors [batch, m, k] x [batch, k, n] with a uniform batch stride."""
+    _require_cuda_f32(a, b)
+    batch, m, k = a.shape
+    _, k2, n = b.shape
+    if k != k2 or b.shape[0] != batch:
+        raise ValueError("shape mismatch")
+    if c is None:
+        c = torch.empty((batch, m, n), dtype=torch.float32, device=a.device)
+    _require_cuda_f32(c)
+    la, lda = _layout_ld(a)
+    lb, ldb = _layout_ld(b)
+    lc, ldc = _layout_ld(c)
+    with torch.cuda.device(a.device):
+        st = load().tcec_sgemm_strided_batched(
+            la, lb, lc, m, n, k, alpha, a.data_ptr(), lda, a.stride(0), b.data_ptr(), ldb, b.stride(0), beta,
+            c.data_ptr(), ldc, c.stride(0), batch, _policy(policy), _stream_ptr())
+    _check(st, "tcec_sgemm_strided_batched")
+    return c
+
+
+def sgemm_batched(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor],
+                  c_list: Sequence[torch.Tensor], *, alpha: float = 1.0, beta: float = 0.0,
+                  policy="fp16_ec") -> Sequence[torch.Tensor]:
+    """Pointer-array batch: one independent matrix per list entry, equal shapes and strides."""
+    batch = len(a_list)
+    if batch == 0:
+        return c_list
+    _require_cuda_f32(*a_list, *b_list, *c_list)
+    m, k = a_list[0].shape
+    _, n = b_list[0].shape
+    la, lda = _layout_ld(a_list[0])
+    lb, ldb = _layout_ld(b_list[0])
+    lc, ldc = _layout_ld(c_list[0])
+    dev = a_list[0].device
+
+    def ptrs(ts):
+        return torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64).to(dev)
+
+    pa, pb, pc = ptrs(a_list), ptrs(b_list), ptrs(c_list)
+    with torch.cuda.device(dev):
+        st = load().tcec_sgemm_batched(la, lb, lc, m, n, k, alpha, pa.data_ptr(), lda, pb.data_ptr(), ldb, beta,
+                                       pc.data_ptr(), ldc, batch, _policy(policy), _stream_ptr())
+        _check(st, "tcec_sgemm_batched")
+        # the pointer tables must outlive the kernels that read them
+        torch.cuda.current_stream().synchronize()
+    return c_list
+
+
+def split(x: torch.Tensor, policy="fp16_ec"):
+    """Element-wise hi / scaled-lo split, widened to float32 (for bit-exact checks)."""
+    _require_cuda_f32(x)
+    x = x.contiguous()
+    hi = torch.empty_like(x)
+    lo = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        st = load().tcec_split(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), x.numel(), _policy(policy), _stream_ptr())
+    _check(st, "tcec_split")
+    return hi, lo
+
+
+def workspace_bytes(m: int, n: int, k: int, batch: int = 1, policy="fp16_ec") -> int:
+    return int(load().tcec_workspace_bytes(m, n, k, batch, _policy(policy)))
+
+
+def destroy() -> None:
+    _check(load().tcec_destroy(), "tcec_destroy")
