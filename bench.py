@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the TCEC SGEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--size S]
+
+One step = one error-corrected SGEMM, C = A * B, M = N = K = S (default 16384, the
+size the throughput target is stated at), FP32 row-major operands, through the
+public call (split of both operands + three-product tcgen05 GEMM).  The headline
+is the fp16 hi/lo policy on U[-1,1) values.  The same shape with the wide-exponent
+values sign * U[1,2) * 2^U{-15..15}, where the tf32 policy is the accurate one and
+fp16 heads overflow, is timed and checked beside it ("wide_exponent" in the JSON
+line).  Throughput is FP32-equivalent: 2*M*N*K flop per GEMM.
+
+With N > 1 (launched by torchrun, one rank per GPU) the GEMM is column-sharded:
+every rank owns an S x S column block of B and of C (weak scaling: N = S * ranks
+columns in total) and A is broadcast from rank 0 with NCCL in row panels, each
+panel's GEMM overlapping the next panel's broadcast.
+
+--impl reference times the reference's CPU path, its FP64 host check loop
+(test/tcec/batch_gemm.cu:561-575), ported in oracle/tcec_oracle.c, on a bounded
+row sample of the same workload with all host threads.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "tcec_sgemm_fp32_equiv_tflops"
+UNIT = "TFLOP/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_burst": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured (MEASURED_PEAKS.json)"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:
+                time.sleep(0.05)
+        except OSError:
+            self.proc = None
+        self.first = 0
+        self.last = None
+
+    def mark_begin(self):
+        self.first = len(self.lines)
+
+    def mark_end(self):
+        self.last = len(self.lines)
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        window = self.lines[self.first:self.last] if self.last and self.last > self.first else self.lines
+        for line in window:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_uniform(torch, device, rows, cols, seed):
+    """U[-1, 1) values."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.rand((rows, cols), generator=g, device=device) * 2.0 - 1.0
+
+
+def make_wide(torch, device, rows, cols, seed):
+    """sign * U[1,2) * 2^e, e uniform integer in -15..15."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    mant = 1.0 + torch.rand((rows, cols), generator=g, device=device)
+    expo = torch.randint(-15, 16, (rows, cols), generator=g, device=device).to(torch.float32)
+    sign = torch.where(torch.rand((rows, cols), generator=g, device=device) < 0.5, -1.0, 1.0)
+    return sign * mant * torch.exp2(expo)
+
+
+def cpu_baseline_sample(size, seconds=12.0, seed=3):
+    """Times the FP64 host loop on a row sample of the workload; returns the baseline dict."""
+    import numpy as np
+
+    from oracle import cpu
+
+    rng = np.random.default_rng(seed)
+
+    def gen(shape):
+        return rng.uniform(-1, 1, shape).astype(np.float32)
+
+    b = gen((size, size))
+    probe_rows = max(cpu.num_threads(), 8)
+    a = gen((probe_rows, size))
+    t0 = time.perf_counter()
+    cpu.gemm_f64(a, b)
+    dt = time.perf_counter() - t0
+    rows = int(min(size, max(probe_rows, probe_rows * seconds / max(dt, 1e-3))))
+    rows = (rows // cpu.num_threads()) * cpu.num_threads() or probe_rows
+    a = gen((rows, size))
+    t0 = time.perf_counter()
+    cpu.gemm_f64(a, b)
+    dt = time.perf_counter() - t0
+    tf = 2.0 * rows * size * size / dt * 1e-12
+    return {"value": tf, "unit": UNIT, "cores": cpu.num_threads(), "kind": "port",
+            "sample": f"{rows} of {size} rows of A against the full {size}x{size} B, FP64 host loop with OpenMP "
+                      f"({dt:.1f} s)"}, rows, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    size = args.size
+    times, rows = [], 0
+    base = None
+    for i in range(args.warmup + args.steps):
+        base, rows, dt = cpu_baseline_sample(size, seconds=max(2.0, 20.0 / max(1, args.steps + args.warmup)))
+        if i >= args.warmup:
+            times.append((rows, dt))
+    flop = sum(2.0 * r * size * size for r, _ in times)
+    secs = sum(dt for _, dt in times)
+    value = flop / secs * 1e-12
+    base["value"] = value
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": secs / max(1, len(times)) * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic", "impl": "reference",
+            "config": {"workload": f"sgemm M=N=K={size} row-major, U[-1,1); bounded row sample",
+                       "policy": "host FP64 check loop (the reference's CPU path)"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_loop(torch, fn, steps, dist_on):
+    """K calls between two events on the current stream; barrier + sync on both sides."""
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier()
+    return e0.elapsed_time(e1)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    from wmma_extension_b200 import sharded, tcec
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path (use --impl reference)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if dist_on:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    tcec.load()
+    peaks = measured_peaks()
+    size = args.size
+    m = n = k = size
+    policy = "fp16_ec"
+
+    a = make_uniform(torch, device, m, k, seed=3) if (rank == 0 or not dist_on) else None
+    b = make_uniform(torch, device, k, n, seed=1003 + rank)
+    c = torch.empty((m, n), dtype=torch.float32, device=device)
+    flop_local = 2.0 * m * n * k
+
+    if dist_on:
+        bufs = [torch.empty((args.panel_rows, k), dtype=torch.float32, device=device) for _ in range(2)] \
+            if rank != 0 else None
+        ops = sharded.cuda_ops(policy)
+
+        def step():
+            sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=args.panel_rows, ops=ops,
+                                         a_buffers=bufs)
+        launches_per_step = 1 + 2 * len(sharded.row_panels(m, args.panel_rows))
+    else:
+        def step():
+            tcec.sgemm(a, b, c, policy=policy)
+        launches_per_step = 3  # split A, split B, GEMM
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    tcec.device_status()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        sampler.mark_begin()
+    ms = time_loop(torch, step, args.steps, dist_on)
+    if rank == 0:
+        sampler.mark_end()
+    clocks = sampler.stop() if rank == 0 else None
+    tcec.device_status()
+    if dist_on:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    ms_per_step = ms / args.steps
+    value = flop_local * world / (ms_per_step * 1e-3) * 1e-12
+
+    extra = {}
+    roofline = None
+    e2e = None
+    cpu_base = None
+    accuracy = None
+    if not dist_on:
+        # ---- dominant kernel alone (operands already split), for the roofline
+        ap, bp = tcec.pack_a(a, policy), tcec.pack_b(b, policy)
+        for _ in range(3):
+            tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy)
+        ms_k = time_loop(torch, lambda: tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy), args.steps, False)
+        achieved = flop_local / (ms_k / args.steps * 1e-3) * 1e-12
+        del ap, bp
+        peak = peaks["bf16_sustained"] / 3.0
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                    "traffic": None,
+                    "peak_is": f"dense 16-bit tensor peak / 3 products, sustained figure, {peaks['source']}",
+                    "frac_of_burst_peak": achieved / (peaks["bf16_burst"] / 3.0),
+                    "kernel": "tcec_gemm_panels_kernel<256,fp16,ec>", "kernel_ms": ms_k / args.steps}
+        # ---- accuracy of the headline on sampled rows (outside any timed region)
+        from oracle import cpu
+        rows = [0, 1, m // 2 - 1, m // 2, m - 1]
+
+        def sampled_errors(aa, bb, pol):
+            a_rows = aa[rows].cpu().numpy()
+            b_host = bb.cpu().numpy()
+            exact = cpu.gemm_f64(a_rows, b_host)
+            tcec.sgemm(aa, bb, c, policy=pol)
+            got = c[rows].cpu().numpy()
+            finite = np.isfinite(got)
+            e = cpu.errors(np.where(finite, got, 0).astype(np.float32), np.where(finite, exact, 0))
+            e32 = cpu.errors(cpu.gemm_f32(a_rows, b_host), exact)
+            return e["max_rel"], float(1.0 - finite.mean()), e32["max_rel"]
+
+        e_h, nf_h, e_f = sampled_errors(a, b, policy)
+        accuracy = {"rows_checked": len(rows), "fp16_ec_max_rel": e_h, "fp32_fma_max_rel": e_f,
+                    "nonfinite_fraction": nf_h}
+        # ---- same shape, wide-exponent values: tf32 policy (accurate) vs fp16 policy (heads overflow)
+        aw, bw = make_wide(torch, device, m, k, seed=3), make_wide(torch, device, k, n, seed=1003)
+        wide = {"values": "sign*U[1,2)*2^U{-15..15}"}
+        for pol in ("tf32_ec", "fp16_ec"):
+            for _ in range(2):
+                tcec.sgemm(aw, bw, c, policy=pol)
+            st = max(2, args.steps // 2)
+            ms_t = time_loop(torch, lambda: tcec.sgemm(aw, bw, c, policy=pol), st, False)
+            e, nf, e32 = sampled_errors(aw, bw, pol)
+            wide[pol] = {"tflops": flop_local / (ms_t / st * 1e-3) * 1e-12, "max_rel_err_finite": e,
+                         "nonfinite_fraction": nf}
+            wide["fp32_fma_max_rel"] = e32
+        wide["tf32_ec"]["frac_of_tf32_roofline"] = wide["tf32_ec"]["tflops"] / (peaks["bf16_sustained"] / 2 / 3)
+        wide["tf32_roofline_is"] = "half the measured 16-bit dense peak (sustained) / 3 products"
+        extra["wide_exponent"] = wide
+        del aw, bw
+        # ---- end to end from pinned host buffers through the public call
+        ah = torch.empty((m, k), dtype=torch.float32, pin_memory=True)
+        bh = torch.empty((k, n), dtype=torch.float32, pin_memory=True)
+        ch = torch.empty((m, n), dtype=torch.float32, pin_memory=True)
+        ah.copy_(a)
+        bh.copy_(b)
+        ad, bd = torch.empty_like(a), torch.empty_like(b)
+
+        def e2e_step():
+            ad.copy_(ah, non_blocking=True)
+            bd.copy_(bh, non_blocking=True)
+            tcec.sgemm(ad, bd, c, policy=policy)
+            ch.copy_(c, non_blocking=True)
+
+        e2e_step()
+        e2e_steps = max(2, min(args.steps, 4))
+        ms_e = time_loop(torch, e2e_step, e2e_steps, False)
+        e2e = {"value": flop_local / (ms_e / e2e_steps * 1e-3) * 1e-12, "unit": UNIT,
+               "h2d_bytes_per_step": 4 * (m * k + k * n), "d2h_bytes_per_step": 4 * m * n,
+               "ms_per_step": ms_e / e2e_steps}
+        del ah, bh, ch, ad, bd
+        tcec.device_status()
+        if rank == 0:
+            cpu_base, _, _ = cpu_baseline_sample(size, seconds=12.0)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16 hi/lo products, f32 accumulate",
+                "data": "synthetic",
+                "config": {"workload": f"sgemm M=N=K={size} per GPU, FP32 row-major A,B, U[-1,1), alpha=1 beta=0",
+                           "policy": policy,
+                           "parallelism": "single GPU" if not dist_on else
+                           f"column-sharded B,C over {world} GPUs (N={size * world}), A broadcast by NCCL in "
+                           f"{args.panel_rows}-row panels inside the timed region",
+                           "l2": "inputs (1 GiB each at 16384) exceed the 126 MB L2; no flush needed",
+                           "promote_k": tcec.get_option("promote_k")},
+                "clocks": clocks, "gpu_launches": launches_per_step * args.steps}
+        if roofline:
+            line["roofline"] = roofline
+        if cpu_base:
+            line["cpu_baseline"] = cpu_base
+        if e2e:
+            line["e2e"] = e2e
+        if accuracy:
+            line["accuracy"] = accuracy
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=16384)
+    ap.add_argument("--panel-rows", type=int, default=2048)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

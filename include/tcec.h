@@ -83,6 +83,27 @@ int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, 
                                void* stream);
 
 /*
+ * Split once, multiply many times.  tcec_pack_a / tcec_pack_b run the split of
+ * load_matrix_sync (include/wmma_extension/tcec/tcec.hpp:194-236) over a whole
+ * operand and store hi (+ scaled lo) in the layout the GEMM kernel streams;
+ * tcec_sgemm_packed is tcec_sgemm on operands packed that way.  `packed` is a
+ * caller-owned device buffer of tcec_packed_bytes(rows, k, policy) bytes, 16-byte
+ * aligned, where rows = m for A and n for B.  The reference re-splits a tile in
+ * every warp that consumes it (test/tcec/batch_gemm.cu:232-255); packing is what
+ * lets one operand (B of a column shard, A after its broadcast) be split once.
+ * A row sub-range of a packed operand that starts at a multiple of 128 rows is
+ * itself a packed operand: it begins tcec_packed_row_offset(row, k, policy) bytes in.
+ */
+size_t tcec_packed_bytes(int rows, int k, int policy);
+size_t tcec_packed_row_offset(int row, int k, int policy);
+int tcec_pack_a(int layout_a, int m, int k, const float* a, long long lda, void* packed, int policy,
+                void* stream);
+int tcec_pack_b(int layout_b, int k, int n, const float* b, long long ldb, void* packed, int policy,
+                void* stream);
+int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void* a_packed,
+                      const void* b_packed, float beta, float* c, long long ldc, int policy, void* stream);
+
+/*
  * Element-wise split, exposed so the split can be checked bit for bit:
  *   hi[i] = cast<T>(in[i]);  lo[i] = cast<T>((in[i] - hi[i]) * s)
  * returned widened to float (lo still carries the scale s = 2^11 for fp16, 1 for
@@ -95,10 +116,11 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
 /*
  * Options (process-wide):
  *   "promote_k"  K extent accumulated inside the tensor-core accumulator before
- *                it is added to the FP32 running sum with a round-to-nearest add
- *                (default 128; 0 = only at the end, the reference's mma_rz_sync
- *                behaviour, include/wmma_extension/tcec/tcec.hpp:773-831; the
- *                reference's mma_rn_sync uses 16 or 8, :640-706).
+ *                it is added to the FP32 running sum with a round-to-nearest add.
+ *                -1 (default) = automatic: 32 to 256 depending on K with error
+ *                correction, 0 without.  0 = only at the end, the reference's
+ *                mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
+ *                the reference's mma_rn_sync uses 16 or 8 (:640-706).
  *   "tile_n"     0 = automatic, 128 or 256.
  */
 int tcec_set_option(const char* name, int value);

@@ -1,0 +1,302 @@
+"""Parity of the CUDA path, called through the C ABI, against the CPU restatement,
+the FP64 ground truth, the reference's golden fixtures and (when oracle/_ref was
+built) the reference's own kernels run live on the same inputs."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu, ref
+from wmma_extension_b200 import tcec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _bits(x):
+    return np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+
+
+def _t(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def _gemm(a, b, **kw):
+    c = tcec.sgemm(_t(a), _t(b), **kw)
+    tcec.device_status()
+    return c.cpu().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _defaults():
+    tcec.set_option("promote_k", -1)
+    tcec.set_option("tile_n", 0)
+    yield
+    tcec.set_option("promote_k", -1)
+    tcec.set_option("tile_n", 0)
+
+
+# ---------------------------------------------------------------- split (bit-exact)
+def test_split_bit_exact_vs_golden_and_oracle(golden_dir):
+    g = np.load(os.path.join(golden_dir, "ref_split.npz"))
+    rng = np.random.default_rng(12)
+    extra = (rng.uniform(-1, 1, 1 << 20) * np.exp2(rng.integers(-40, 20, 1 << 20))).astype(np.float32)
+    for name in ("fp16", "tf32"):
+        hi, lo = tcec.split(_t(g["x"]), name + "_ec")
+        assert np.array_equal(_bits(hi.cpu().numpy()), _bits(g["hi_" + name]))
+        assert np.array_equal(_bits(lo.cpu().numpy()), _bits(g["lo_" + name]))
+        hi, lo = tcec.split(_t(extra), name + "_ec")
+        ohi, olo = cpu.split(extra, name + "_ec")
+        assert np.array_equal(_bits(hi.cpu().numpy()), _bits(ohi))
+        assert np.array_equal(_bits(lo.cpu().numpy()), _bits(olo))
+
+
+def test_packed_panels_hold_the_oracle_split():
+    """The operand panels the GEMM kernel streams contain exactly the oracle's hi / lo bits."""
+    rng = np.random.default_rng(13)
+    m, k = 200, 70
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    for layout in ("row", "col"):
+        at = _t(a) if layout == "row" else _t(a.T).t()
+        packed = tcec.pack_a(at, "fp16_ec").cpu().numpy()
+        ohi, olo = cpu.split(a, "fp16_ec")
+        nkb = (k + 31) // 32
+        blocks = packed.reshape(-1, nkb, 2, 16, 4, 8, 16).view(np.float16)  # [rb][kb][hi/lo][r8][c][r%8][8 halves]
+        # element (r, kk): rb=r//128, r8=(r%128)//8, rr=r%8, kb=kk//32, c=(kk%32)//8, e=kk%8
+        r, kk = np.meshgrid(np.arange(m), np.arange(k), indexing="ij")
+        got_hi = blocks[r // 128, kk // 32, 0, (r % 128) // 8, (kk % 32) // 8, r % 8, kk % 8].astype(np.float32)
+        got_lo = blocks[r // 128, kk // 32, 1, (r % 128) // 8, (kk % 32) // 8, r % 8, kk % 8].astype(np.float32)
+        assert np.array_equal(_bits(got_hi), _bits(ohi)), layout
+        assert np.array_equal(_bits(got_lo), _bits(olo)), layout
+
+
+# ---------------------------------------------------------------- GEMM vs oracle / FP64
+POLICY_BOUND = {"fp16_ec": 1e-6, "tf32_ec": 1e-6, "fp16_no_ec": 2e-3, "tf32_no_ec": 2e-3}
+
+
+@pytest.mark.parametrize("policy", list(POLICY_BOUND))
+@pytest.mark.parametrize("shape", [(16, 16, 16), (32, 32, 32), (128, 256, 64), (256, 512, 256), (37, 41, 19),
+                                   (1, 1, 1), (130, 257, 33), (129, 127, 515), (512, 384, 1000)])
+def test_gemm_matches_oracle(policy, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(100 + m + n + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    exact = cpu.gemm_f64(a, b)
+    got = _gemm(a, b, policy=policy)
+    pk = 32 if k <= 512 else 64  # the library's automatic promotion interval for these K
+    want = cpu.tcec_gemm(a, b, policy=policy, rn_block=pk // (16 if policy.startswith("fp16") else 8))
+    e_got, e_orc = cpu.errors(got, exact), cpu.errors(want, exact)
+    assert e_got["max_rel"] < POLICY_BOUND[policy]
+    if policy.endswith("no_ec"):
+        assert e_got["max_rel"] < 2 * e_orc["max_rel"] + 1e-6
+    else:
+        # same split bits, same products; only the accumulator roundings may differ
+        assert np.max(np.abs(got - want)) <= 1e-6 * max(1.0, np.max(np.abs(exact)))
+        e_f32 = cpu.errors(cpu.gemm_f32(a, b), exact)
+        assert e_got["max_rel"] <= 2 * max(e_orc["max_rel"], e_f32["max_rel"])
+        if m == n == k == 32:
+            assert e_got["max_abs"] < 1e-5  # the reference's unit-test threshold (test/tcec/mma.cu:8)
+
+
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+@pytest.mark.parametrize("lc", ["row", "col"])
+def test_layouts_alpha_beta_and_padded_leading_dimensions(la, lb, lc):
+    rng = np.random.default_rng(31)
+    m, n, k = 200, 300, 100
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+
+    def view(x, layout, pad):
+        r, c = x.shape
+        if layout == "row":
+            buf = torch.full((r, c + pad), float("nan"), device=DEV)
+            buf[:, :c] = _t(x)
+            return buf[:, :c]
+        buf = torch.full((c, r + pad), float("nan"), device=DEV)
+        buf[:, :r] = _t(x.T)
+        return buf[:, :r].t()
+
+    for pad in (0, 4, 3):  # 3: leading dimension not a multiple of 4 -> scalar paths
+        A, B, C = view(a, la, pad), view(b, lb, pad), view(c0, lc, pad)
+        tcec.sgemm(A, B, C, alpha=1.5, beta=0.5)
+        tcec.device_status()
+        want = 1.5 * cpu.gemm_f64(a, b) + 0.5 * c0
+        assert cpu.errors(C.cpu().numpy(), want)["max_rel"] < 1e-6, (la, lb, lc, pad)
+        assert torch.isnan(C.as_strided((C._base.shape), C._base.stride())).sum() == (
+            C._base.numel() - m * n), "wrote outside the matrix"
+
+
+def test_beta_zero_never_reads_c_and_alpha_zero_scales():
+    rng = np.random.default_rng(32)
+    a = rng.uniform(-1, 1, (64, 64)).astype(np.float32)
+    b = rng.uniform(-1, 1, (64, 64)).astype(np.float32)
+    c = torch.full((64, 64), float("nan"), device=DEV)
+    tcec.sgemm(_t(a), _t(b), c, beta=0.0)
+    assert torch.isfinite(c).all()
+    c2 = torch.ones(64, 64, device=DEV)
+    tcec.sgemm(_t(a), _t(b), c2, alpha=0.0, beta=3.0)
+    assert torch.equal(c2, torch.full_like(c2, 3.0))
+    c3 = torch.full((64, 64), float("nan"), device=DEV)
+    tcec.sgemm(_t(a[:, :0]), _t(b[:0, :]), c3, beta=0.0)  # k == 0
+    assert torch.equal(c3, torch.zeros_like(c3))
+    tcec.device_status()
+
+
+def test_promotion_interval_option():
+    """promote_k = 0 reproduces the in-accumulator (round-toward-zero) variant; the default beats it."""
+    rng = np.random.default_rng(33)
+    a = rng.uniform(0, 1, (256, 4096)).astype(np.float32)
+    b = rng.uniform(0, 1, (4096, 256)).astype(np.float32)
+    exact = cpu.gemm_f64(a, b)
+    errs = {}
+    for pk in (0, 32, 128, 512):
+        tcec.set_option("promote_k", pk)
+        errs[pk] = cpu.errors(_gemm(a, b), exact)["max_rel"]
+    e_f32 = cpu.errors(cpu.gemm_f32(a, b), exact)["max_rel"]
+    assert errs[128] < e_f32 and errs[32] < e_f32
+    assert errs[0] > 4 * errs[128]
+
+
+def test_tile_width_option_gives_same_quality():
+    rng = np.random.default_rng(34)
+    a = rng.standard_normal((256, 512)).astype(np.float32)
+    b = rng.standard_normal((512, 512)).astype(np.float32)
+    exact = cpu.gemm_f64(a, b)
+    for tn in (128, 256):
+        tcec.set_option("tile_n", tn)
+        assert cpu.errors(_gemm(a, b), exact)["max_rel"] < 1e-6
+
+
+# ---------------------------------------------------------------- golden fixtures of the reference
+def test_against_reference_warp_fixtures(golden_dir):
+    g = np.load(os.path.join(golden_dir, "ref_warp_mma.npz"))
+    a, b, c = g["a"], g["b"], g["c"]
+    for name in ("fp16", "tf32"):
+        got = _gemm(a, b, policy=name + "_ec")
+        assert np.max(np.abs(got - g[f"d_{name}_mma_ec_abd_default"])) < 4e-6
+        got_c = tcec.sgemm(_t(a), _t(b), _t(c).clone(), beta=1.0, policy=name + "_ec").cpu().numpy()
+        assert np.max(np.abs(got_c - g[f"d_{name}_mma_ec_abcd_default"])) < 4e-6
+        got_n = _gemm(a, b, policy=name + "_no_ec")
+        assert np.max(np.abs(got_n - g[f"d_{name}_mma_noec_abd_default"])) < 4e-6
+
+
+def test_against_reference_bgemm_fixtures(golden_dir):
+    g = np.load(os.path.join(golden_dir, "ref_bgemm.npz"))
+    a, b = g["a"], g["b"]
+    for name in ("fp16", "tf32"):
+        got = tcec.sgemm_strided_batched(_t(a), _t(b), policy=name + "_ec").cpu().numpy()
+        for i in range(a.shape[0]):
+            exact = cpu.gemm_f64(a[i], b[i])
+            e_ref = cpu.errors(g["c_" + name][i], exact)["max_rel"]
+            e_got = cpu.errors(got[i], exact)["max_rel"]
+            assert e_got <= 2 * e_ref
+    got = _gemm(g["a_iota"][0], g["b_iota"][0])
+    exact = cpu.gemm_f64(g["a_iota"][0], g["b_iota"][0])
+    assert cpu.errors(got, exact)["fro_rel"] <= 2 * cpu.errors(g["c_iota_fp16"][0], exact)["fro_rel"] + 1e-9
+    tcec.device_status()
+
+
+# ---------------------------------------------------------------- batched forms
+def test_batched_forms_agree_and_match_fp64():
+    rng = np.random.default_rng(4)
+    batch, m, n, k = 12, 256, 256, 256
+    a = rng.standard_normal((batch, m, k)).astype(np.float32)
+    b = rng.standard_normal((batch, k, n)).astype(np.float32)
+    at, bt = _t(a), _t(b)
+    c_str = tcec.sgemm_strided_batched(at, bt)
+    c_list = [torch.empty(m, n, device=DEV) for _ in range(batch)]
+    tcec.sgemm_batched(list(at.unbind(0)), list(bt.unbind(0)), c_list)
+    tcec.device_status()
+    assert torch.equal(torch.stack(c_list), c_str)
+    for i in (0, batch // 2, batch - 1):
+        single = tcec.sgemm(at[i], bt[i])
+        assert torch.equal(single, c_str[i])  # batching does not change a single bit
+        assert cpu.errors(c_str[i].cpu().numpy(), cpu.gemm_f64(a[i], b[i]))["max_rel"] < 1e-6
+
+
+def test_ragged_batch_shapes():
+    rng = np.random.default_rng(41)
+    for (batch, m, n, k) in [(3, 100, 60, 50), (1, 129, 257, 31), (5, 16, 16, 16)]:
+        a = rng.standard_normal((batch, m, k)).astype(np.float32)
+        b = rng.standard_normal((batch, k, n)).astype(np.float32)
+        got = tcec.sgemm_strided_batched(_t(a), _t(b)).cpu().numpy()
+        for i in range(batch):
+            assert cpu.errors(got[i], cpu.gemm_f64(a[i], b[i]))["max_rel"] < 1e-6
+    tcec.device_status()
+
+
+def test_packed_entry_points_match_plain_call():
+    rng = np.random.default_rng(42)
+    m, n, k = 384, 300, 200
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    at, bt = _t(a), _t(b)
+    want = tcec.sgemm(at, bt)
+    ap, bp = tcec.pack_a(at), tcec.pack_b(bt)
+    assert torch.equal(tcec.sgemm_packed(ap, bp, m, n, k), want)
+    # a row sub-range of packed A is itself a packed A
+    off = tcec.packed_row_offset(128, k)
+    part = tcec.sgemm_packed(ap[off:], bp, m - 128, n, k)
+    assert torch.equal(part, want[128:])
+    tcec.device_status()
+
+
+# ---------------------------------------------------------------- live reference comparator
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref was not built")
+@pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec"])
+@pytest.mark.parametrize("dist_name", ["uniform", "normal", "positive"])
+def test_error_no_worse_than_twice_the_reference(policy, dist_name):
+    """Acceptance bound: max relative error vs FP64 <= 2x the reference TCEC kernel's and
+    <= 2x an FP32 SGEMM's, on identical inputs."""
+    torch.manual_seed(50)
+    m, n, k = 1024, 768, 4096
+    if dist_name == "uniform":
+        a, b = torch.rand(m, k, device=DEV) * 2 - 1, torch.rand(k, n, device=DEV) * 2 - 1
+    elif dist_name == "normal":
+        a, b = torch.randn(m, k, device=DEV), torch.randn(k, n, device=DEV)
+    else:
+        a, b = torch.rand(m, k, device=DEV), torch.rand(k, n, device=DEV)
+    exact = a.double() @ b.double()
+    scale = exact.abs().max()
+
+    def err(c):
+        return ((c.double() - exact).abs().max() / scale).item()
+
+    e_ref = err(ref.bgemm(a[None], b[None], tf32=policy.startswith("tf32"), per=4)[0])
+    e_got = err(tcec.sgemm(a, b, policy=policy))
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    e_f32 = err(a @ b)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    tcec.device_status()
+    assert e_got <= 2 * e_ref, (e_got, e_ref)
+    assert e_got <= 2 * e_f32, (e_got, e_f32)
+
+
+# ---------------------------------------------------------------- full-size properties
+def test_full_size_sampled_rows_and_linearity():
+    """M=N=K=16384-class problem checked through size-independent properties: sampled rows
+    against the FP64 host GEMM, and linearity in alpha."""
+    torch.manual_seed(3)
+    n = 8192
+    sign = torch.where(torch.rand(n, n, device=DEV) < 0.5, -1.0, 1.0)
+    a = sign * (1 + torch.rand(n, n, device=DEV)) * torch.exp2(torch.randint(-15, 16, (n, n), device=DEV).float())
+    b = torch.randn(n, n, device=DEV)
+    a.clamp_(-65000, 65000)  # keep fp16 heads finite so both policies can be compared
+    rows = [0, 1, 127, 128, 4095, 4096, 8191]
+    a_rows = a[rows].cpu().numpy()
+    bh = b.cpu().numpy()
+    exact = cpu.gemm_f64(a_rows, bh)
+    for policy in ("tf32_ec", "fp16_ec"):
+        c = tcec.sgemm(a, b, policy=policy)
+        tcec.device_status()
+        e = cpu.errors(c[rows].cpu().numpy(), exact)
+        e32 = cpu.errors(cpu.gemm_f32(a_rows, bh), exact)
+        assert e["max_rel"] <= 2 * e32["max_rel"], (policy, e, e32)
+        c2 = tcec.sgemm(a, b, alpha=2.0, policy=policy)
+        assert torch.equal(c2, 2 * c)  # scaling by a power of two is exact
+        del c, c2

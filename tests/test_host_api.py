@@ -1,0 +1,95 @@
+"""Host-side checks that need no GPU: the C ABI loads, exports what include/tcec.h
+declares, and rejects bad arguments before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from wmma_extension_b200 import tcec
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "tcec.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tcec_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = tcec.load()
+    names = declared_functions()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(tcec.EXPORTED_SYMBOLS) <= set(names)
+
+
+def test_version_and_status_strings():
+    lib = tcec.load()
+    assert b"sm_100a" in lib.tcec_version()
+    assert tcec.status_string(tcec.OK) == "ok"
+    assert "argument" in tcec.status_string(tcec.ERR_INVALID_ARGUMENT)
+    assert "wait" in tcec.status_string(tcec.ERR_TIMEOUT)
+
+
+def test_invalid_arguments_are_rejected_without_a_device():
+    lib = tcec.load()
+    z = None
+    # unknown layout, negative size, bad policy, leading dimension too small, missing pointer
+    assert lib.tcec_sgemm(7, 0, 0, 4, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_sgemm(0, 0, 0, -1, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_sgemm(0, 0, 0, 4, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 9, z) == tcec.ERR_INVALID_ARGUMENT
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.tcec_sgemm(0, 0, 0, 4, 4, 4, 1.0, p, 3, p, 4, 0.0, p, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_sgemm(0, 0, 0, 4, 4, 4, 1.0, p, 4, p, 4, 0.0, p, 2, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_sgemm(0, 0, 0, 4, 4, 4, 1.0, z, 4, p, 4, 0.0, p, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    # empty problems are fine and launch nothing
+    assert lib.tcec_sgemm(0, 0, 0, 0, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 0, z) == tcec.OK
+    assert lib.tcec_sgemm_batched(0, 0, 0, 4, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 0, 0, z) == tcec.OK
+    assert lib.tcec_split(z, z, z, 0, 0, z) == tcec.OK
+    assert lib.tcec_split(z, z, z, 5, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_pack_a(0, 4, 4, z, 4, z, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_sgemm_packed(0, 4, 4, 4, 1.0, z, z, 0.0, z, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+
+
+def test_options_round_trip():
+    old = tcec.get_option("promote_k")
+    try:
+        assert old == -1  # automatic by default
+        tcec.set_option("promote_k", 64)
+        assert tcec.get_option("promote_k") == 64
+        with pytest.raises(tcec.TcecError):
+            tcec.set_option("promote_k", -2)
+        with pytest.raises(tcec.TcecError):
+            tcec.set_option("tile_n", 96)
+        with pytest.raises(tcec.TcecError):
+            tcec.set_option("no_such_option", 1)
+    finally:
+        tcec.set_option("promote_k", old)
+
+
+def test_workspace_and_packed_sizes():
+    # fp16+ec: hi and lo, 2 bytes each -> 4 bytes per padded element
+    assert tcec.packed_bytes(4096, 4096, "fp16_ec") == 4096 * 4096 * 4
+    assert tcec.packed_bytes(4096, 4096, "fp16_no_ec") == 4096 * 4096 * 2
+    assert tcec.packed_bytes(4096, 4096, "tf32_ec") == 4096 * 4096 * 8
+    assert tcec.packed_bytes(1, 1, "fp16_ec") == 256 * 32 * 4  # padded to 256 rows x one k block
+    assert tcec.workspace_bytes(4096, 4096, 4096) == 2 * 4096 * 4096 * 4
+    assert tcec.packed_row_offset(128, 64, "fp16_ec") * 2 == tcec.packed_bytes(256, 64, "fp16_ec")
+    assert tcec.packed_row_offset(100, 64, "fp16_ec") == 0  # not a multiple of 128
+
+
+def test_layout_detection():
+    import torch
+
+    a = torch.zeros(6, 4)
+    assert tcec._layout_ld(a) == (tcec.ROW_MAJOR, 4)
+    assert tcec._layout_ld(a.t()) == (tcec.COL_MAJOR, 4)
+    assert tcec._layout_ld(torch.zeros(6, 8)[:, :4]) == (tcec.ROW_MAJOR, 8)
+    with pytest.raises(ValueError):
+        tcec._layout_ld(torch.zeros(6, 8)[:, ::2])
+    with pytest.raises(ValueError):
+        tcec.sgemm(torch.zeros(2, 2), torch.zeros(2, 2))  # CPU tensors: there is no CPU path

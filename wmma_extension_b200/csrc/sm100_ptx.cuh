@@ -53,15 +53,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. `abort_flag` is a CTA-shared word any role may raise; a waiter
-// that sees it raised, or that runs out of polls, returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+// Bounded waits.  `abort_flag` is a CTA-shared word any role may raise; a waiter that sees
+// it raised, or that runs out of polls, returns false.
+//
+// Every poll of an mbarrier is a shared-memory access, and the tensor pipe's operand reads
+// already use most shared-memory cycles (96 of 128 bytes per clock for a 128x256x16 MMA), so a
+// thread spinning on try_wait measurably slows the MMAs.  All waiters therefore sleep between
+// polls; `ns` is chosen per role from the slack that role has.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t ns = 64) {
   for (uint32_t i = 0; i < TCEC_WAIT_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (ns) __nanosleep(ns);
     if ((i & 0x3ff) == 0x3ff && *abort_flag) return false;
   }
   return false;
+}
+// Warp-collective form: lane 0 polls, the result is broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t ns = 128) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, ns);
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 
 // Bounded wait that ignores the abort word: used on the way out, by a role that
@@ -166,6 +179,17 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Re-balance the register file between warpgroups (all four warps of a warpgroup
+// must execute the same instruction).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
 // ---------------------------------------------------------------- descriptors

@@ -30,8 +30,10 @@ struct DeviceState {
 
 std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
-int g_promote_k = 128;
+int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
+int g_debug_flags = 0;
+unsigned long long* g_trace = nullptr;
 
 #define TCEC_CUDA(call)                        \
   do {                                         \
@@ -93,20 +95,39 @@ int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out
 
 struct Shape {
   int tile_n, tiles_m, tiles_n, nkb, kop, np;
-  size_t a_bytes, b_bytes;  // per matrix
+  int a_row_blocks, b_row_blocks;  // 128-row panel blocks, padded to an even count
+  size_t a_bytes, b_bytes;         // per matrix
 };
+bool policy_tf32(int policy) { return policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC; }
+bool policy_ec(int policy) { return policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC; }
+int padded_row_blocks(int rows) { return ((rows + 255) / 256) * 2; }
+size_t packed_bytes(int rows, int k, int policy) {
+  const int kop = policy_tf32(policy) ? 16 : 32;
+  const size_t nkb = (k + kop - 1) / kop;
+  return static_cast<size_t>(padded_row_blocks(rows)) * nkb * (policy_ec(policy) ? 2 : 1) * kPanelBytes;
+}
+// K extent the tensor-core accumulator may gather before the round-to-nearest add, in k blocks.
+// Automatic choice: short products are dominated by the accumulator's truncation, so they are
+// promoted more often (every 32 of K up to K = 512, 64 up to 2048, 128 up to 4096, else 256); the
+// policies without error correction keep the reference's default for them, accumulation inside
+// the tensor core (mma_rz_sync, include/wmma_extension/tcec/detail/no_cor.hpp:858-897).
+int promote_blocks(int k, int policy, int kop) {
+  int pk = g_promote_k;
+  if (pk < 0) pk = !policy_ec(policy) ? 0 : (k <= 512 ? 32 : (k <= 2048 ? 64 : (k <= 4096 ? 128 : 256)));
+  return pk > 0 ? (pk + kop - 1) / kop : 0;
+}
 Shape plan(int m, int n, int k, int policy) {
   Shape s;
-  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
-  const bool ec = (policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC);
-  s.kop = tf32 ? 16 : 32;
-  s.np = ec ? 2 : 1;
+  s.kop = policy_tf32(policy) ? 16 : 32;
+  s.np = policy_ec(policy) ? 2 : 1;
   s.tile_n = g_tile_n ? g_tile_n : (n > 128 ? 256 : 128);
   s.tiles_m = (m + 127) / 128;
   s.tiles_n = (n + s.tile_n - 1) / s.tile_n;
   s.nkb = (k + s.kop - 1) / s.kop;
-  s.a_bytes = static_cast<size_t>(s.tiles_m) * s.nkb * s.np * kPanelBytes;
-  s.b_bytes = static_cast<size_t>(s.tiles_n) * (s.tile_n / 128) * s.nkb * s.np * kPanelBytes;
+  s.a_row_blocks = padded_row_blocks(m);
+  s.b_row_blocks = padded_row_blocks(n);
+  s.a_bytes = packed_bytes(m, k, policy);
+  s.b_bytes = packed_bytes(n, k, policy);
   return s;
 }
 
@@ -156,6 +177,89 @@ void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
 
 bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
 
+// Split one operand (A: rows = m; B: rows = n) into panels on `stream`.
+void pack_operand(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
+                  long long ld, long long stride, int batch, uint8_t* panels, size_t panels_stride,
+                  int policy, cudaStream_t stream) {
+  const int kop = policy_tf32(policy) ? 16 : 32;
+  SplitParams sp{};
+  sp.src = src;
+  sp.src_array = src_array;
+  sp.ld = ld;
+  sp.batch_stride = stride;
+  sp.rows = rows;
+  sp.k = k;
+  sp.k_contiguous = k_contiguous ? 1 : 0;
+  sp.row_blocks = padded_row_blocks(rows);
+  sp.nkb = (k + kop - 1) / kop;
+  sp.panels = panels;
+  sp.panels_batch_stride = static_cast<long long>(panels_stride);
+  sp.mul = 1.0f;
+  if (policy_tf32(policy)) {
+    if (policy_ec(policy)) launch_split<true, true>(sp, batch, stream);
+    else launch_split<true, false>(sp, batch, stream);
+  } else {
+    if (policy_ec(policy)) launch_split<false, true>(sp, batch, stream);
+    else launch_split<false, false>(sp, batch, stream);
+  }
+}
+
+void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t* panels_a,
+                 size_t a_stride, const uint8_t* panels_b, size_t b_stride, float beta, float* c,
+                 float* const* c_array, long long ldc, long long stride_c, int lc, int batch,
+                 int policy, const DeviceState* st, cudaStream_t stream) {
+  GemmPanelParams gp{};
+  gp.M = m;
+  gp.N = n;
+  gp.K = k;
+  gp.batch = batch;
+  gp.nkb = s.nkb;
+  gp.tiles_m = s.tiles_m;
+  gp.tiles_n = s.tiles_n;
+  gp.promo = promote_blocks(k, policy, s.kop);
+  gp.alpha = alpha;
+  gp.beta = beta;
+  gp.panels_a = panels_a;
+  gp.panels_b = panels_b;
+  gp.panels_a_batch_stride = static_cast<long long>(a_stride);
+  gp.panels_b_batch_stride = static_cast<long long>(b_stride);
+  gp.c = c;
+  gp.c_array = c_array;
+  gp.ldc = ldc;
+  gp.c_batch_stride = stride_c;
+  gp.c_col_major = (lc == TCEC_COL_MAJOR);
+  gp.status = st->status;
+  gp.debug_flags = g_debug_flags;
+  gp.trace = g_trace;
+  const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
+#define TCEC_DISPATCH(T, E)                                      \
+  do {                                                           \
+    if (s.tile_n == 256)                                         \
+      launch_gemm<256, T, E>(gp, st->sm_count, stream);          \
+    else                                                         \
+      launch_gemm<128, T, E>(gp, st->sm_count, stream);          \
+  } while (0)
+  if (tf32 && ec)
+    TCEC_DISPATCH(true, true);
+  else if (tf32)
+    TCEC_DISPATCH(true, false);
+  else if (ec)
+    TCEC_DISPATCH(false, true);
+  else
+    TCEC_DISPATCH(false, false);
+#undef TCEC_DISPATCH
+}
+
+int scale_only(float beta, float* c, float* const* c_array, long long ldc, long long stride_c, int m,
+               int n, int lc, int batch, cudaStream_t stream) {
+  if (beta == 1.f) return TCEC_OK;
+  const int inner = lc == TCEC_COL_MAJOR ? m : n, outer = lc == TCEC_COL_MAJOR ? n : m;
+  dim3 grid((inner + 255) / 256, outer < 65535 ? outer : 65535, batch);
+  scale_c_kernel<<<grid, 256, 0, stream>>>(c, c_array, ldc, stride_c, m, n, lc == TCEC_COL_MAJOR, beta);
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
 int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const float* a,
               const float* const* a_array, long long lda, long long stride_a, const float* b,
               const float* const* b_array, long long ldb, long long stride_b, float beta, float* c,
@@ -179,93 +283,20 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
   DeviceState* st = nullptr;
   int rc = get_device_state(&st);
   if (rc != TCEC_OK) return rc;
-
-  if (k == 0 || alpha == 0.f) {
-    if (beta == 1.f) return TCEC_OK;
-    const int inner = lc == TCEC_COL_MAJOR ? m : n, outer = lc == TCEC_COL_MAJOR ? n : m;
-    dim3 grid((inner + 255) / 256, outer < 65535 ? outer : 65535, batch);
-    scale_c_kernel<<<grid, 256, 0, stream>>>(c, c_array, ldc, stride_c, m, n, lc == TCEC_COL_MAJOR,
-                                             beta);
-    TCEC_CUDA(cudaGetLastError());
-    return TCEC_OK;
-  }
+  if (k == 0 || alpha == 0.f) return scale_only(beta, c, c_array, ldc, stride_c, m, n, lc, batch, stream);
 
   const Shape s = plan(m, n, k, policy);
-  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
-  const bool ec = (policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC);
   void* ws = nullptr;
   rc = get_workspace(st, stream, (s.a_bytes + s.b_bytes) * batch, &ws);
   if (rc != TCEC_OK) return rc;
   uint8_t* panels_a = static_cast<uint8_t*>(ws);
   uint8_t* panels_b = panels_a + s.a_bytes * batch;
-
-  SplitParams spa{};
-  spa.src = a;
-  spa.src_array = a_array;
-  spa.ld = lda;
-  spa.batch_stride = stride_a;
-  spa.rows = m;
-  spa.k = k;
-  spa.k_contiguous = (la == TCEC_ROW_MAJOR);
-  spa.row_blocks = s.tiles_m;
-  spa.nkb = s.nkb;
-  spa.panels = panels_a;
-  spa.panels_batch_stride = static_cast<long long>(s.a_bytes);
-  spa.mul = 1.0f;
-  SplitParams spb{};
-  spb.src = b;
-  spb.src_array = b_array;
-  spb.ld = ldb;
-  spb.batch_stride = stride_b;
-  spb.rows = n;
-  spb.k = k;
-  spb.k_contiguous = (lb == TCEC_COL_MAJOR);
-  spb.row_blocks = s.tiles_n * (s.tile_n / 128);
-  spb.nkb = s.nkb;
-  spb.panels = panels_b;
-  spb.panels_batch_stride = static_cast<long long>(s.b_bytes);
-  spb.mul = 1.0f;
-
-  GemmPanelParams gp{};
-  gp.M = m;
-  gp.N = n;
-  gp.K = k;
-  gp.batch = batch;
-  gp.nkb = s.nkb;
-  gp.tiles_m = s.tiles_m;
-  gp.tiles_n = s.tiles_n;
-  gp.promo = g_promote_k > 0 ? (g_promote_k + s.kop - 1) / s.kop : 0;
-  gp.alpha = alpha;
-  gp.beta = beta;
-  gp.panels_a = panels_a;
-  gp.panels_b = panels_b;
-  gp.panels_a_batch_stride = static_cast<long long>(s.a_bytes);
-  gp.panels_b_batch_stride = static_cast<long long>(s.b_bytes);
-  gp.c = c;
-  gp.c_array = c_array;
-  gp.ldc = ldc;
-  gp.c_batch_stride = stride_c;
-  gp.c_col_major = (lc == TCEC_COL_MAJOR);
-  gp.status = st->status;
-
-#define TCEC_DISPATCH(T, E)                                      \
-  do {                                                           \
-    launch_split<T, E>(spa, batch, stream);                      \
-    launch_split<T, E>(spb, batch, stream);                      \
-    if (s.tile_n == 256)                                         \
-      launch_gemm<256, T, E>(gp, st->sm_count, stream);          \
-    else                                                         \
-      launch_gemm<128, T, E>(gp, st->sm_count, stream);          \
-  } while (0)
-  if (tf32 && ec)
-    TCEC_DISPATCH(true, true);
-  else if (tf32)
-    TCEC_DISPATCH(true, false);
-  else if (ec)
-    TCEC_DISPATCH(false, true);
-  else
-    TCEC_DISPATCH(false, false);
-#undef TCEC_DISPATCH
+  pack_operand(la == TCEC_ROW_MAJOR, m, k, a, a_array, lda, stride_a, batch, panels_a, s.a_bytes, policy,
+               stream);
+  pack_operand(lb == TCEC_COL_MAJOR, n, k, b, b_array, ldb, stride_b, batch, panels_b, s.b_bytes, policy,
+               stream);
+  gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
+              lc, batch, policy, st, stream);
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
 }
@@ -298,6 +329,65 @@ int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, 
                    nullptr, ldb, stride_b, beta, c, nullptr, ldc, stride_c, batch, policy, stream);
 }
 
+size_t tcec_packed_bytes(int rows, int k, int policy) {
+  if (rows <= 0 || k <= 0 || policy < 0 || policy > 3) return 0;
+  return packed_bytes(rows, k, policy);
+}
+
+size_t tcec_packed_row_offset(int row, int k, int policy) {
+  if (row < 0 || row % 128 != 0 || k <= 0 || policy < 0 || policy > 3) return 0;
+  return packed_bytes(256, k, policy) / 2 * static_cast<size_t>(row / 128);
+}
+
+static int pack_entry(bool is_b, int layout, int rows, int k, const float* src, long long ld, void* packed,
+                      int policy, void* stream) {
+  if (bad_layout(layout) || rows < 0 || k < 0 || policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
+  if (rows == 0 || k == 0) return TCEC_OK;
+  if (!src || !packed) return TCEC_ERR_INVALID_ARGUMENT;
+  // A is rows x k, B is k x rows
+  const bool k_contig = is_b ? (layout == TCEC_COL_MAJOR) : (layout == TCEC_ROW_MAJOR);
+  if (ld < (k_contig ? k : rows)) return TCEC_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(packed) & 15) != 0) return TCEC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = nullptr;
+  const int rc = get_device_state(&st);
+  if (rc != TCEC_OK) return rc;
+  pack_operand(k_contig, rows, k, src, nullptr, ld, 0, 1, static_cast<uint8_t*>(packed), 0, policy,
+               static_cast<cudaStream_t>(stream));
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
+int tcec_pack_a(int layout_a, int m, int k, const float* a, long long lda, void* packed, int policy,
+                void* stream) {
+  return pack_entry(false, layout_a, m, k, a, lda, packed, policy, stream);
+}
+
+int tcec_pack_b(int layout_b, int k, int n, const float* b, long long ldb, void* packed, int policy,
+                void* stream) {
+  return pack_entry(true, layout_b, n, k, b, ldb, packed, policy, stream);
+}
+
+int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void* a_packed,
+                      const void* b_packed, float beta, float* c, long long ldc, int policy, void* stream) {
+  if (bad_layout(layout_c) || m < 0 || n < 0 || k < 0 || policy < 0 || policy > 3)
+    return TCEC_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0) return TCEC_OK;
+  if (!c || ldc < (layout_c == TCEC_ROW_MAJOR ? n : m)) return TCEC_ERR_INVALID_ARGUMENT;
+  if (k > 0 && (!a_packed || !b_packed)) return TCEC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = nullptr;
+  const int rc = get_device_state(&st);
+  if (rc != TCEC_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (k == 0 || alpha == 0.f) return scale_only(beta, c, nullptr, ldc, 0, m, n, layout_c, 1, s);
+  const Shape sh = plan(m, n, k, policy);
+  gemm_packed(sh, m, n, k, alpha, static_cast<const uint8_t*>(a_packed), 0,
+              static_cast<const uint8_t*>(b_packed), 0, beta, c, nullptr, ldc, 0, layout_c, 1, policy, st, s);
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
 int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, void* stream) {
   if (policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
   if (count == 0) return TCEC_OK;
@@ -308,7 +398,7 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
     const int rc = get_device_state(&st);
     if (rc != TCEC_OK) return rc;
   }
-  const bool tf32 = (policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC);
+  const bool tf32 = policy_tf32(policy);
   const size_t want = (count + 255) / 256;
   const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
   if (tf32)
@@ -319,17 +409,28 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
   return TCEC_OK;
 }
 
+// Development aid, not part of the declared ABI: device buffer of 6 * 4096 u64 for hand-off timestamps.
+int tcec_debug_set_trace(unsigned long long* dev_buffer) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_trace = dev_buffer;
+  return TCEC_OK;
+}
+
 int tcec_set_option(const char* name, int value) {
   if (!name) return TCEC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(g_mu);
   if (!strcmp(name, "promote_k")) {
-    if (value < 0) return TCEC_ERR_INVALID_ARGUMENT;
+    if (value < -1) return TCEC_ERR_INVALID_ARGUMENT;
     g_promote_k = value;
     return TCEC_OK;
   }
   if (!strcmp(name, "tile_n")) {
     if (value != 0 && value != 128 && value != 256) return TCEC_ERR_INVALID_ARGUMENT;
     g_tile_n = value;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "debug_flags")) {
+    g_debug_flags = value;
     return TCEC_OK;
   }
   return TCEC_ERR_INVALID_ARGUMENT;

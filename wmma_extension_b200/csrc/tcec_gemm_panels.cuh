@@ -5,7 +5,10 @@
 //   main  : A_hi*B_hi accumulates in TMEM for `promo` k-blocks, then is added to
 //           an FP32 register accumulator with a round-to-nearest FADD (the
 //           reference does this every 16 of K because the tensor-core
-//           accumulator truncates; the interval here is a launch parameter);
+//           accumulator truncates; the interval here is a launch parameter).
+//           The main and the correction products are issued by two different
+//           threads, so the correction stream keeps the tensor pipe busy while
+//           the main stream waits for the epilogue to drain its accumulator;
 //   corr  : A_lo*B_hi + A_hi*B_lo accumulates in a second TMEM region for the
 //           whole K loop, as in the reference;
 //   store : C = alpha * (main + corr / 2^11) + beta * C   (tf32: corr / 1).
@@ -13,8 +16,12 @@
 //
 // One persistent CTA per SM.  Roles by warp:
 //   warp 0      producer  - linear bulk copies of operand panels into a ring
-//   warp 1      MMA       - one elected thread issues tcgen05.mma, owns TMEM
+//   warp 1      MMA main  - one thread issues the A_hi*B_hi products; owns TMEM
+//   warp 2      MMA corr  - one thread issues the A_lo*B_hi and A_hi*B_lo products
 //   warps 4..   epilogue  - tcgen05.ld, RN promotion, fold, alpha/beta, stores
+// (issuing an MMA, a commit or a barrier wait costs the issuing thread 50 to 200
+// cycles each, so a single thread cannot keep a 128-cycle MMA pipe fed with six
+// MMAs, a commit and a wait per k block; two threads can.)
 // All hand-offs are mbarriers; every wait is bounded and raises `status`.
 #pragma once
 #include "sm100_ptx.cuh"
@@ -37,6 +44,8 @@ struct GemmPanelParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;             // device word; non-zero after a wait ran out
+  int debug_flags;         // timing experiments only: bit 0 = reuse resident stages (results invalid)
+  unsigned long long* trace;  // optional: CTA 0 writes clock64() at hand-off points (6 roles x 4096 slots)
 };
 
 enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3 };
@@ -58,6 +67,9 @@ struct GemmPanelCfg {
   static constexpr int GROUP_M = 16;                   // m tiles per raster group
 };
 
+__device__ __forceinline__ void trace_mark(const GemmPanelParams& p, int role, uint32_t idx) {
+  if (p.trace && blockIdx.x == 0 && idx < 4096) p.trace[role * 4096 + idx] = clock64();
+}
 struct TileCoord {
   int b, mt, nt;
 };
@@ -83,7 +95,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   constexpr int NST = Cfg::NST;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[NST], bar_empty[NST];
-  __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain;
+  __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_flag;
 
@@ -94,13 +106,14 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), kEc ? 2 : 1);  // one commit per issuing thread
     }
     mbar_init(smem_u32(&bar_main_full), 1);
     mbar_init(smem_u32(&bar_main_free), Cfg::EPI_WARPS);
     mbar_init(smem_u32(&bar_corr_full), 1);
     mbar_init(smem_u32(&bar_corr_free), Cfg::EPI_WARPS);
-    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_init(smem_u32(&bar_drain[0]), 1);
+    mbar_init(smem_u32(&bar_drain[1]), 1);
     abort_flag = 0;
     fence_mbar_init();
   }
@@ -115,10 +128,11 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   const uint32_t tmem_corr = tmem_base_s + BN;
   volatile uint32_t* abortp = &abort_flag;
 
+  if (warp < 4) {
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       uint32_t armed = 0, armed_parity = 0;  // per stage: a copy was issued, and in which phase
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
@@ -127,14 +141,17 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
                             static_cast<size_t>(tc.mt) * p.nkb * Cfg::A_BYTES;
         const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
                             static_cast<size_t>(tc.nt) * Cfg::NB * p.nkb * (kPanelBytes * Cfg::NP);
-        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          const uint32_t s = it % NST, ph = (it / NST) & 1;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp)) {
+        for (int kb = 0; kb < p.nkb; ++kb, ++it, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp, 128)) {
             ok = false;
             break;
           }
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
+          if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {
+            mbar_arrive(full);
+            continue;
+          }
           mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
@@ -153,77 +170,117 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         abort_flag = 1;
         atomicCAS(p.status, 0, kErrProducerWait);
         // Let this thread's own copies land before the CTA gives up its shared memory.
-        for (uint32_t s = 0; s < static_cast<uint32_t>(NST); ++s)
-          if (armed & (1u << s)) mbar_wait_plain(smem_u32(&bar_full[s]), (armed_parity >> s) & 1);
+        for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
+          if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_full[q]), (armed_parity >> q) & 1);
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ MMA issuer, main products
+    // Kept to a handful of integer instructions per MMA: descriptors are a constant OR-ed
+    // with a 14-bit address field, ring positions and the promotion interval are counters.
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
-      uint32_t it = 0, chunk = 0, tcount = 0;
+      const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+      constexpr uint32_t kBHi = Cfg::A_BYTES >> 4;
+      const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
+      uint32_t it = 0, s = 0, ph = 0, chunk = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        int left_in_chunk = 0;  // k blocks still to issue in the current chunk
         for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          const uint32_t s = it % NST, ph = (it / NST) & 1;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
             ok = false;
             break;
           }
-          const bool first_in_chunk = p.promo ? (kb % p.promo == 0) : (kb == 0);
+          trace_mark(p, 0, it);
+          const bool first_in_chunk = (left_in_chunk == 0);
           if (first_in_chunk) {
-            if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp)) {
+            const int rest = p.nkb - kb;
+            left_in_chunk = (p.promo && p.promo < rest) ? p.promo : rest;
+            if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp, 0)) {
               ok = false;
               break;
             }
+            trace_mark(p, 1, chunk);
           }
           tc_fence_after();
-          const uint32_t a_hi = smem_base + s * Cfg::STAGE_BYTES;
-          const uint32_t a_lo = a_hi + kPanelBytes;
-          const uint32_t b_hi = a_hi + Cfg::A_BYTES;
-          const uint32_t b_lo = b_hi + Cfg::NB * kPanelBytes;
+          const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            umma_ss<kTf32>(tmem_main, umma_desc_kmajor_noswizzle(a_hi + 256 * j, 128, 512),
-                           umma_desc_kmajor_noswizzle(b_hi + 256 * j, 128, 512), idesc,
+          for (uint32_t j = 0; j < 2; ++j)
+            umma_ss<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
                            (first_in_chunk && j == 0) ? 0u : 1u);
-          const bool last_in_chunk = (kb == p.nkb - 1) || (p.promo && ((kb + 1) % p.promo == 0));
-          if (last_in_chunk) {
+          if (--left_in_chunk == 0) {
             umma_commit(smem_u32(&bar_main_full));
             ++chunk;
           }
-          if constexpr (kEc) {
-            if (kb == 0) {
-              if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-            }
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              umma_ss<kTf32>(tmem_corr, umma_desc_kmajor_noswizzle(a_lo + 256 * j, 128, 512),
-                             umma_desc_kmajor_noswizzle(b_hi + 256 * j, 128, 512), idesc,
-                             (kb == 0 && j == 0) ? 0u : 1u);
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              umma_ss<kTf32>(tmem_corr, umma_desc_kmajor_noswizzle(a_hi + 256 * j, 128, 512),
-                             umma_desc_kmajor_noswizzle(b_lo + 256 * j, 128, 512), idesc, 1u);
-          }
           umma_commit(smem_u32(&bar_empty[s]));
+          trace_mark(p, 5, it);
+          if (++s == static_cast<uint32_t>(NST)) {
+            s = 0;
+            ph ^= 1;
+          }
         }
-        if (!ok) break;
-        if constexpr (kEc) umma_commit(smem_u32(&bar_corr_full));
       }
       if (!ok) {
         abort_flag = 1;
         atomicCAS(p.status, 0, kErrMmaWait);
         // Nothing may still be writing TMEM when it is released below.
-        umma_commit(smem_u32(&bar_drain));
-        mbar_wait_plain(smem_u32(&bar_drain), 0);
+        umma_commit(smem_u32(&bar_drain[0]));
+        mbar_wait_plain(smem_u32(&bar_drain[0]), 0);
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ MMA issuer, correction products
+    if constexpr (kEc) {
+      if (lane == 0) {
+        const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
+        const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+        constexpr uint32_t kALo = kPanelBytes >> 4, kBHi = Cfg::A_BYTES >> 4,
+                           kBLo = (Cfg::A_BYTES + Cfg::NB * kPanelBytes) >> 4;
+        const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
+        uint32_t s = 0, ph = 0, tcount = 0, cit = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+          for (int kb = 0; kb < p.nkb; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
+              ok = false;
+              break;
+            }
+            if (kb == 0) {
+              if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
+                ok = false;
+                break;
+              }
+            }
+            trace_mark(p, 4, cit++);
+            tc_fence_after();
+            const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+#pragma unroll
+            for (uint32_t j = 0; j < 2; ++j)
+              umma_ss<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
+                             (kb == 0 && j == 0) ? 0u : 1u);
+#pragma unroll
+            for (uint32_t j = 0; j < 2; ++j)
+              umma_ss<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
+            umma_commit(smem_u32(&bar_empty[s]));
+            if (++s == static_cast<uint32_t>(NST)) {
+              s = 0;
+              ph ^= 1;
+            }
+          }
+          if (!ok) break;
+          umma_commit(smem_u32(&bar_corr_full));
+        }
+        if (!ok) {
+          abort_flag = 1;
+          atomicCAS(p.status, 0, kErrMmaWait);
+          umma_commit(smem_u32(&bar_drain[1]));
+          mbar_wait_plain(smem_u32(&bar_drain[1]), 0);
+        }
+      }
+    }
+  }
+  } else {
     // ------------------------------------------------------------ epilogue
     const int ew = warp - 4;
     const int q = warp & 3;          // TMEM lane quarter this warp may read
@@ -238,10 +295,11 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
       float acc[128];
       for (int c = 0; c < nchunks; ++c, ++chunk) {
-        if (!mbar_wait(smem_u32(&bar_main_full), chunk & 1, abortp)) {
+        if (!mbar_wait_warp(smem_u32(&bar_main_full), chunk & 1, abortp)) {
           ok = false;
           break;
         }
+        if (warp == 4 && lane == 0) trace_mark(p, 2, chunk);
         tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -259,10 +317,11 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_main_free));
+        if (warp == 4 && lane == 0) trace_mark(p, 3, chunk);
       }
       if (!ok) break;
       if constexpr (kEc) {
-        if (!mbar_wait(smem_u32(&bar_corr_full), tcount & 1, abortp)) {
+        if (!mbar_wait_warp(smem_u32(&bar_corr_full), tcount & 1, abortp)) {
           ok = false;
           break;
         }

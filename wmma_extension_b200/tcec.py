@@ -27,6 +27,11 @@ EXPORTED_SYMBOLS = (
     "tcec_sgemm",
     "tcec_sgemm_batched",
     "tcec_sgemm_strided_batched",
+    "tcec_packed_bytes",
+    "tcec_packed_row_offset",
+    "tcec_pack_a",
+    "tcec_pack_b",
+    "tcec_sgemm_packed",
     "tcec_split",
     "tcec_set_option",
     "tcec_get_option",
@@ -64,6 +69,16 @@ def load() -> ctypes.CDLL:
     lib.tcec_sgemm_batched.restype = i
     lib.tcec_sgemm_strided_batched.argtypes = [i, i, i, i, i, i, f, p, ll, ll, p, ll, ll, f, p, ll, ll, i, i, p]
     lib.tcec_sgemm_strided_batched.restype = i
+    lib.tcec_packed_bytes.argtypes = [i, i, i]
+    lib.tcec_packed_bytes.restype = sz
+    lib.tcec_packed_row_offset.argtypes = [i, i, i]
+    lib.tcec_packed_row_offset.restype = sz
+    lib.tcec_pack_a.argtypes = [i, i, i, p, ll, p, i, p]
+    lib.tcec_pack_a.restype = i
+    lib.tcec_pack_b.argtypes = [i, i, i, p, ll, p, i, p]
+    lib.tcec_pack_b.restype = i
+    lib.tcec_sgemm_packed.argtypes = [i, i, i, i, f, p, p, f, p, ll, i, p]
+    lib.tcec_sgemm_packed.restype = i
     lib.tcec_split.argtypes = [p, p, p, sz, i, p]
     lib.tcec_split.restype = i
     lib.tcec_set_option.argtypes = [ctypes.c_char_p, i]
@@ -208,6 +223,55 @@ def sgemm_batched(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor]
         # the pointer tables must outlive the kernels that read them
         torch.cuda.current_stream().synchronize()
     return c_list
+
+
+def packed_bytes(rows: int, k: int, policy="fp16_ec") -> int:
+    return int(load().tcec_packed_bytes(rows, k, _policy(policy)))
+
+
+def packed_row_offset(row: int, k: int, policy="fp16_ec") -> int:
+    return int(load().tcec_packed_row_offset(row, k, _policy(policy)))
+
+
+def pack_a(a: torch.Tensor, policy="fp16_ec", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Split A (m x k) once into operand panels; returns the uint8 panel buffer."""
+    _require_cuda_f32(a)
+    m, k = a.shape
+    la, lda = _layout_ld(a)
+    if out is None:
+        out = torch.empty(packed_bytes(m, k, policy), dtype=torch.uint8, device=a.device)
+    with torch.cuda.device(a.device):
+        st = load().tcec_pack_a(la, m, k, a.data_ptr(), lda, out.data_ptr(), _policy(policy), _stream_ptr())
+    _check(st, "tcec_pack_a")
+    return out
+
+
+def pack_b(b: torch.Tensor, policy="fp16_ec", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Split B (k x n) once into operand panels; returns the uint8 panel buffer."""
+    _require_cuda_f32(b)
+    k, n = b.shape
+    lb, ldb = _layout_ld(b)
+    if out is None:
+        out = torch.empty(packed_bytes(n, k, policy), dtype=torch.uint8, device=b.device)
+    with torch.cuda.device(b.device):
+        st = load().tcec_pack_b(lb, k, n, b.data_ptr(), ldb, out.data_ptr(), _policy(policy), _stream_ptr())
+    _check(st, "tcec_pack_b")
+    return out
+
+
+def sgemm_packed(a_packed: torch.Tensor, b_packed: torch.Tensor, m: int, n: int, k: int,
+                 c: Optional[torch.Tensor] = None, *, alpha: float = 1.0, beta: float = 0.0,
+                 policy="fp16_ec") -> torch.Tensor:
+    """C = alpha * A @ B + beta * C on operands packed by pack_a / pack_b."""
+    if c is None:
+        c = torch.empty((m, n), dtype=torch.float32, device=a_packed.device)
+    _require_cuda_f32(c)
+    lc, ldc = _layout_ld(c)
+    with torch.cuda.device(c.device):
+        st = load().tcec_sgemm_packed(lc, m, n, k, alpha, a_packed.data_ptr(), b_packed.data_ptr(), beta,
+                                      c.data_ptr(), ldc, _policy(policy), _stream_ptr())
+    _check(st, "tcec_sgemm_packed")
+    return c
 
 
 def split(x: torch.Tensor, policy="fp16_ec"):
