@@ -219,7 +219,8 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     if dist_on:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     tcec.load()
     peaks = measured_peaks()
     size = args.size
@@ -251,9 +252,10 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        for _ in range(2):
-            step()
-        torch.cuda.synchronize()
+    for _ in range(2):  # every rank: the steps contain collectives
+        step()
+    torch.cuda.synchronize()
+    if rank == 0:
         sampler.mark_begin()
     ms = time_loop(torch, step, args.steps, dist_on)
     if rank == 0:

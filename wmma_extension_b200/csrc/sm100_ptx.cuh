@@ -100,7 +100,7 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-// Tiled 3-D load (x fastest). No multicast: every CTA fetches its own tile.
+// Tiled 3-D load (x fastest). Every CTA fetches its own tile.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int x,
                                             int y, int z) {
   asm volatile(
