@@ -33,6 +33,7 @@ extern "C" {
 #define TCEC_ERR_CUDA 3
 #define TCEC_ERR_TIMEOUT 4 /* a bounded device-side wait ran out */
 #define TCEC_ERR_ALLOC 5
+#define TCEC_ERR_TOO_LARGE 6 /* tcec_sgemm_static only: operands exceed TCEC_STATIC_SCRATCH_BYTES */
 
 /* storage order of a matrix: element (i,j) at i*ld + j (row) or i + j*ld (col) */
 #define TCEC_ROW_MAJOR 0
@@ -81,6 +82,36 @@ int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, 
                                const float* b, long long ldb, long long stride_b, float beta,
                                float* c, long long ldc, long long stride_c, int batch, int policy,
                                void* stream);
+
+/*
+ * tcec_sgemm without any allocation.  This entry point has no counterpart in the reference.
+ *
+ * For callers that cannot call cudaMalloc when they need the product - a process whose memory
+ * pool already owns the device, a latency-critical loop that must stay off the allocator's
+ * locks, a plugin host that forbids allocation after start-up.  Same arguments, result and
+ * rounding as tcec_sgemm; the split operands go to a fixed TCEC_STATIC_SCRATCH_BYTES array that
+ * is part of the library's device image (each GPU that loads the library holds it until the
+ * process ends) instead of a cudaMalloc'ed workspace, and the call makes no cudaMalloc, cudaFree
+ * or other allocating call, on the device or on the host.
+ *
+ * Limit: tcec_packed_bytes(m, k, policy) + tcec_packed_bytes(n, k, policy) must not exceed
+ * TCEC_STATIC_SCRATCH_BYTES (e.g. up to 2048 x 2048 x 2048 with the fp16 policies, half of that
+ * K with tf32); larger problems return TCEC_ERR_TOO_LARGE and launch nothing.
+ *
+ * The first call on a device looks up the array's device address and sets kernel attributes;
+ * make that first call outside any stream capture.  All calls on a device share the one array
+ * and it keeps the previous call's panels: two calls whose kernels overlap on the GPU (different
+ * streams without an ordering between them) race and give wrong results - order them.  Nothing
+ * in the array needs clearing between calls; every byte the GEMM reads is rewritten first.
+ * Bounded-wait expiry is reported by tcec_static_status(), the counterpart of
+ * tcec_device_status() for this entry point.
+ */
+#define TCEC_STATIC_SCRATCH_BYTES (32u << 20)
+int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+                      const float* a, long long lda, const float* b, long long ldb, float beta, float* c,
+                      long long ldc, int policy, void* stream);
+size_t tcec_static_scratch_bytes(void);
+int tcec_static_status(int* detail);
 
 /*
  * Split once, multiply many times.  tcec_pack_a / tcec_pack_b run the split of

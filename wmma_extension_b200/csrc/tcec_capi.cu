@@ -492,6 +492,123 @@ int tcec_destroy(void) {
   return TCEC_OK;
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+//
+// Some callers may not allocate device memory at the moment they need a GEMM: code running
+// under a memory pool that owns the whole device, a real-time loop that must not take the
+// allocator's locks, a plugin whose host forbids cudaMalloc after start-up.  For them the
+// operand panels (the scratch the GEMM kernel streams from) live in a fixed array inside this
+// library's device image instead of a workspace obtained with cudaMalloc, and so does the
+// status word the kernels raise when a bounded wait runs out.  Every GPU that loads the
+// library holds the array until the process exits.
+//
+// In host code the array's name is only a handle for the runtime, not a device address, so
+// the address is looked up once per device with cudaGetSymbolAddress, with that device current.
+static __device__ __align__(256) unsigned char g_static_panels[TCEC_STATIC_SCRATCH_BYTES];
+static __device__ int g_static_status_word;
+
+namespace {
+constexpr int kMaxStaticDevices = 64;
+struct StaticDevice {
+  bool ready = false;
+  uint8_t* panels = nullptr;
+  int* status = nullptr;
+  int sm_count = 0;
+};
+StaticDevice g_static_dev[kMaxStaticDevices];  // fixed table: nothing is allocated on the host either
+
+int static_device_state(StaticDevice** out) {
+  int dev = 0;
+  TCEC_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxStaticDevices) return TCEC_ERR_UNSUPPORTED;
+  StaticDevice& sd = g_static_dev[dev];
+  if (!sd.ready) {
+    int major = 0;
+    TCEC_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return TCEC_ERR_UNSUPPORTED;
+    TCEC_CUDA(cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_panels) != cudaSuccess || p == nullptr) return TCEC_ERR_CUDA;
+    sd.panels = static_cast<uint8_t*>(p);
+    p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_status_word) != cudaSuccess || p == nullptr) return TCEC_ERR_CUDA;
+    sd.status = static_cast<int*>(p);
+    // opting the kernels into their dynamic shared memory size changes a function attribute; it allocates nothing
+    TCEC_CUDA((set_smem_attr<128, false, false>()));
+    TCEC_CUDA((set_smem_attr<128, false, true>()));
+    TCEC_CUDA((set_smem_attr<128, true, false>()));
+    TCEC_CUDA((set_smem_attr<128, true, true>()));
+    TCEC_CUDA((set_smem_attr<256, false, false>()));
+    TCEC_CUDA((set_smem_attr<256, false, true>()));
+    TCEC_CUDA((set_smem_attr<256, true, false>()));
+    TCEC_CUDA((set_smem_attr<256, true, true>()));
+    sd.ready = true;
+  }
+  *out = &sd;
+  return TCEC_OK;
+}
+}  // namespace
+
+size_t tcec_static_scratch_bytes(void) { return TCEC_STATIC_SCRATCH_BYTES; }
+
+int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+                      const float* a, long long lda, const float* b, long long ldb, float beta, float* c,
+                      long long ldc, int policy, void* stream_v) {
+  if (bad_layout(layout_a) || bad_layout(layout_b) || bad_layout(layout_c)) return TCEC_ERR_INVALID_ARGUMENT;
+  if (m < 0 || n < 0 || k < 0 || policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0) return TCEC_OK;
+  if (!c || ldc < (layout_c == TCEC_ROW_MAJOR ? n : m)) return TCEC_ERR_INVALID_ARGUMENT;
+  if (k > 0) {
+    if (!a || !b) return TCEC_ERR_INVALID_ARGUMENT;
+    if (lda < (layout_a == TCEC_ROW_MAJOR ? k : m)) return TCEC_ERR_INVALID_ARGUMENT;
+    if (ldb < (layout_b == TCEC_ROW_MAJOR ? n : k)) return TCEC_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (k == 0 || alpha == 0.f) {
+    StaticDevice* sd0 = nullptr;
+    const int rc0 = static_device_state(&sd0);
+    if (rc0 != TCEC_OK) return rc0;
+    return scale_only(beta, c, nullptr, ldc, 0, m, n, layout_c, 1, stream);
+  }
+  const Shape s = plan(m, n, k, policy);
+  if (s.a_bytes + s.b_bytes > TCEC_STATIC_SCRATCH_BYTES) return TCEC_ERR_TOO_LARGE;
+  StaticDevice* sd = nullptr;
+  const int rc = static_device_state(&sd);
+  if (rc != TCEC_OK) return rc;
+  // Nothing in the array has to start at zero: the two split kernels below write every byte of
+  // every panel the GEMM reads (rows and K beyond the matrix are written as zeros), and the
+  // status word is only ever raised, never relied on to be clear by the kernels.
+  uint8_t* panels_a = sd->panels;
+  uint8_t* panels_b = sd->panels + s.a_bytes;  // a_bytes is a multiple of 8192
+  pack_operand(layout_a == TCEC_ROW_MAJOR, m, k, a, nullptr, lda, 0, 1, panels_a, 0, policy, stream);
+  pack_operand(layout_b == TCEC_COL_MAJOR, n, k, b, nullptr, ldb, 0, 1, panels_b, 0, policy, stream);
+  DeviceState view;  // launch parameters only; owns nothing
+  view.status = sd->status;
+  view.sm_count = sd->sm_count;
+  gemm_packed(s, m, n, k, alpha, panels_a, 0, panels_b, 0, beta, c, nullptr, ldc, 0, layout_c, 1, policy, &view,
+              stream);
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
+int tcec_static_status(int* detail) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  StaticDevice* sd = nullptr;
+  const int rc = static_device_state(&sd);
+  if (rc != TCEC_OK) return rc;
+  TCEC_CUDA(cudaDeviceSynchronize());
+  int word = 0;
+  TCEC_CUDA(cudaMemcpy(&word, sd->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (detail) *detail = word;
+  if (word != 0) {
+    const int zero = 0;
+    TCEC_CUDA(cudaMemcpy(sd->status, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    return TCEC_ERR_TIMEOUT;
+  }
+  return TCEC_OK;
+}
+
 const char* tcec_status_string(int status) {
   switch (status) {
     case TCEC_OK: return "ok";
@@ -500,6 +617,7 @@ const char* tcec_status_string(int status) {
     case TCEC_ERR_CUDA: return "CUDA runtime error";
     case TCEC_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case TCEC_ERR_ALLOC: return "workspace allocation failed";
+    case TCEC_ERR_TOO_LARGE: return "operands exceed the fixed scratch of the allocation-free entry point";
     default: return "unknown status";
   }
 }

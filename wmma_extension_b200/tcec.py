@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(_HERE, "libtcec_b200.so")
 
 ROW_MAJOR, COL_MAJOR = 0, 1
 POLICIES = {"fp16_ec": 0, "tf32_ec": 1, "fp16_no_ec": 2, "tf32_no_ec": 3}
-OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_ALLOC = range(6)
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_ALLOC, ERR_TOO_LARGE = range(7)
 
 EXPORTED_SYMBOLS = (
     "tcec_sgemm",
@@ -33,6 +33,9 @@ EXPORTED_SYMBOLS = (
     "tcec_pack_b",
     "tcec_sgemm_packed",
     "tcec_split",
+    "tcec_sgemm_static",
+    "tcec_static_scratch_bytes",
+    "tcec_static_status",
     "tcec_set_option",
     "tcec_get_option",
     "tcec_device_status",
@@ -79,6 +82,12 @@ def load() -> ctypes.CDLL:
     lib.tcec_pack_b.restype = i
     lib.tcec_sgemm_packed.argtypes = [i, i, i, i, f, p, p, f, p, ll, i, p]
     lib.tcec_sgemm_packed.restype = i
+    lib.tcec_sgemm_static.argtypes = [i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, p]
+    lib.tcec_sgemm_static.restype = i
+    lib.tcec_static_scratch_bytes.argtypes = []
+    lib.tcec_static_scratch_bytes.restype = sz
+    lib.tcec_static_status.argtypes = [ctypes.POINTER(i)]
+    lib.tcec_static_status.restype = i
     lib.tcec_split.argtypes = [p, p, p, sz, i, p]
     lib.tcec_split.restype = i
     lib.tcec_set_option.argtypes = [ctypes.c_char_p, i]
@@ -173,6 +182,39 @@ def sgemm(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *,
                                c.data_ptr(), ldc, _policy(policy), _stream_ptr())
     _check(st, "tcec_sgemm")
     return c
+
+
+def sgemm_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1.0, beta: float = 0.0,
+                 policy="fp16_ec") -> torch.Tensor:
+    """``sgemm`` through the entry point that allocates nothing (``tcec_sgemm_static``).
+
+    For callers that cannot allocate device memory when they need the product; the split
+    operands go to a fixed array inside the library, so the problem must fit it
+    (``TcecError`` with ``ERR_TOO_LARGE`` otherwise) and ``c`` must be supplied.  Calls that
+    overlap on the GPU share that array and race: keep them on one stream.
+    """
+    _require_cuda_f32(a, b, c)
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2 or tuple(c.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    la, lda = _layout_ld(a)
+    lb, ldb = _layout_ld(b)
+    lc, ldc = _layout_ld(c)
+    with torch.cuda.device(a.device):
+        st = load().tcec_sgemm_static(la, lb, lc, m, n, k, alpha, a.data_ptr(), lda, b.data_ptr(), ldb, beta,
+                                      c.data_ptr(), ldc, _policy(policy), _stream_ptr())
+    _check(st, "tcec_sgemm_static")
+    return c
+
+
+def static_status() -> int:
+    """Synchronise and raise if a kernel launched by ``sgemm_static`` gave up a bounded wait."""
+    detail = ctypes.c_int(0)
+    st = load().tcec_static_status(ctypes.byref(detail))
+    if st != OK:
+        raise TcecError(st, f"static status word {detail.value}")
+    return detail.value
 
 
 def sgemm_strided_batched(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *,
