@@ -148,7 +148,7 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  * Options (process-wide):
  *   "promote_k"  K extent accumulated inside the tensor-core accumulator before
  *                it is added to the FP32 running sum with a round-to-nearest add.
- *                -1 (default) = automatic: 32 to 256 depending on K with error
+ *                -1 (default) = automatic: 32 to 512 depending on K with error
  *                correction, 0 without.  0 = only at the end, the reference's
  *                mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
  *                the reference's mma_rn_sync uses 16 or 8 (:640-706).

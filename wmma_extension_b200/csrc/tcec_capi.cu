@@ -108,12 +108,14 @@ size_t packed_bytes(int rows, int k, int policy) {
 }
 // K extent the tensor-core accumulator may gather before the round-to-nearest add, in k blocks.
 // Automatic choice: short products are dominated by the accumulator's truncation, so they are
-// promoted more often (every 32 of K up to K = 512, 64 up to 2048, 128 up to 4096, else 256); the
+// promoted more often (every 64 of K up to K = 2048, 128 up to 4096, 256 below
+// 16384, else 512; each step keeps the error within the reference kernel's on identical inputs,
+// all-positive inputs included, where the truncation bias is largest); the
 // policies without error correction keep the reference's default for them, accumulation inside
 // the tensor core (mma_rz_sync, include/wmma_extension/tcec/detail/no_cor.hpp:858-897).
 int promote_blocks(int k, int policy, int kop) {
   int pk = g_promote_k;
-  if (pk < 0) pk = !policy_ec(policy) ? 0 : (k <= 512 ? 32 : (k <= 2048 ? 64 : (k <= 4096 ? 128 : 256)));
+  if (pk < 0) pk = !policy_ec(policy) ? 0 : (k <= 2048 ? 64 : (k <= 4096 ? 128 : (k < 16384 ? 256 : 512)));
   return pk > 0 ? (pk + kop - 1) / kop : 0;
 }
 Shape plan(int m, int n, int k, int policy) {

@@ -316,6 +316,76 @@ def sgemm_packed(a_packed: torch.Tensor, b_packed: torch.Tensor, m: int, n: int,
     return c
 
 
+_host_ctx = {}
+
+
+def sgemm_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, *, policy="fp16_ec",
+               panel_rows: int = 2048, device: Optional[torch.device] = None) -> torch.Tensor:
+    """C = A @ B for operands in (pinned) HOST memory; the result is written to ``c_host``.
+
+    B is copied and split once; A travels in row panels, so that the copy-in of panel p+1, the
+    GEMM on panel p and the copy-out of panel p-1 overlap on three streams (PCIe is full duplex).
+    Returns after the last copy-out has completed.  Device staging buffers are cached per shape.
+    """
+    for t in (a_host, b_host, c_host):
+        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError("host operands must be contiguous float32 CPU tensors")
+    m, k = a_host.shape
+    k2, n = b_host.shape
+    if k != k2 or tuple(c_host.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    panel_rows = max(128, (min(panel_rows, m) + 127) // 128 * 128)
+    key = (dev.index, m, n, k, panel_rows, _policy(policy))
+    ctx = _host_ctx.get(key)
+    if ctx is None:
+        _host_ctx.clear()  # one cached shape at a time
+        with torch.cuda.device(dev):
+            ctx = {
+                "s_in": torch.cuda.Stream(), "s_out": torch.cuda.Stream(),
+                "b": torch.empty((k, n), dtype=torch.float32, device=dev),
+                "bp": torch.empty(packed_bytes(n, k, policy), dtype=torch.uint8, device=dev),
+                "a": [torch.empty((panel_rows, k), dtype=torch.float32, device=dev) for _ in range(2)],
+                "ap": [torch.empty(packed_bytes(panel_rows, k, policy), dtype=torch.uint8, device=dev)
+                       for _ in range(2)],
+                "c": [torch.empty((panel_rows, n), dtype=torch.float32, device=dev) for _ in range(2)],
+            }
+        _host_ctx[key] = ctx
+    with torch.cuda.device(dev):
+        cur = torch.cuda.current_stream()
+        s_in, s_out = ctx["s_in"], ctx["s_out"]
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            ctx["b"].copy_(b_host, non_blocking=True)
+            e_b = s_in.record_event()
+        cur.wait_event(e_b)
+        pack_b(ctx["b"], policy, out=ctx["bp"])
+        a_free = [None, None]   # compute finished reading a[i]
+        c_done = [None, None]   # copy-out finished reading c[i]
+        for p, r0 in enumerate(range(0, m, panel_rows)):
+            rows = min(panel_rows, m - r0)
+            i = p % 2
+            with torch.cuda.stream(s_in):
+                if a_free[i] is not None:
+                    s_in.wait_event(a_free[i])
+                ctx["a"][i][:rows].copy_(a_host[r0:r0 + rows], non_blocking=True)
+                e_a = s_in.record_event()
+            cur.wait_event(e_a)
+            pack_a(ctx["a"][i][:rows], policy, out=ctx["ap"][i])
+            a_free[i] = cur.record_event()
+            if c_done[i] is not None:
+                cur.wait_event(c_done[i])
+            sgemm_packed(ctx["ap"][i], ctx["bp"], rows, n, k, ctx["c"][i][:rows], policy=policy)
+            e_c = cur.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(e_c)
+                c_host[r0:r0 + rows].copy_(ctx["c"][i][:rows], non_blocking=True)
+                c_done[i] = s_out.record_event()
+        cur.wait_stream(s_out)
+    return c_host
+
+
 def split(x: torch.Tensor, policy="fp16_ec"):
     """Element-wise hi / scaled-lo split, widened to float32 (for bit-exact checks)."""
     _require_cuda_f32(x)
