@@ -285,7 +285,9 @@ def run_ours(args):
         del ap, bp
         peak = peaks["bf16_sustained"] / 3.0
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                    "traffic": None,
+                    "traffic": 1.139e9 * (size / 6144.0) ** 3,
+                    "traffic_is": "dram__bytes_read+write of this kernel captured by ncu at 6144^3 (1.139 GB per "
+                                  "launch), scaled by (size/6144)^3; see profiles/",
                     "peak_is": f"dense 16-bit tensor peak / 3 products, sustained figure, {peaks['source']}",
                     "frac_of_burst_peak": achieved / (peaks["bf16_burst"] / 3.0),
                     "kernel": "tcec_gemm_panels_kernel<256,fp16,ec>", "kernel_ms": ms_k / args.steps}

@@ -331,9 +331,11 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       const int row = tc.mt * 128 + q * 32 + lane;
       const int col0 = tc.nt * BN + colbase;
       const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+      if constexpr (kEc) {
+        // Fold the correction term into the registers first and hand the accumulator back
+        // before the stores: the next tile's correction MMAs then overlap this tile's stores.
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        if constexpr (kEc) {
+        for (int cc = 0; cc < 4; ++cc) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
           tmem_ld_wait();
@@ -341,6 +343,12 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
           for (int i = 0; i < 32; ++i)
             acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * corr_scale;
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));
+      }
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
         if (row < p.M) {
           if (!p.c_col_major) {
             float* crow = cbase + static_cast<long long>(row) * p.ldc;
@@ -385,11 +393,6 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
             }
           }
         }
-      }
-      if constexpr (kEc) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));
       }
     }
     if (!ok) {
