@@ -153,6 +153,12 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
  *                the reference's mma_rn_sync uses 16 or 8 (:640-706).
  *   "tile_n"     0 = automatic, 128 or 256.
+ *   "path"       0 = automatic; 1 = always split the operands into panels first, then multiply
+ *                (two kernels; the faster one whenever the tensor pipe is the limit); 2 = use
+ *                the single kernel that TMA-loads FP32 tiles and splits them in registers
+ *                whenever the call allows it (fp16 policies, n > 128, 16-byte aligned operands
+ *                with leading dimensions that are multiples of 4, no pointer arrays).
+ *                Automatic picks it for batches with k <= 512, which are bound by DRAM traffic.
  */
 int tcec_set_option(const char* name, int value);
 int tcec_get_option(const char* name, int* value);

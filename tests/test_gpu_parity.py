@@ -32,9 +32,11 @@ def _gemm(a, b, **kw):
 def _defaults():
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
+    tcec.set_option("path", 0)
     yield
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
+    tcec.set_option("path", 0)
 
 
 # ---------------------------------------------------------------- split (bit-exact)
@@ -169,6 +171,55 @@ def test_tile_width_option_gives_same_quality():
     for tn in (128, 256):
         tcec.set_option("tile_n", tn)
         assert cpu.errors(_gemm(a, b), exact)["max_rel"] < 1e-6
+
+
+# ---------------------------------------------------------------- FP32-tile (in-kernel split) path
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+@pytest.mark.parametrize("shape", [(128, 256, 32), (200, 300, 100), (37, 260, 19), (384, 512, 1000)])
+def test_fp32_tile_kernel_matches_panel_kernel(la, lb, shape):
+    """The kernel that TMA-loads FP32 tiles and splits them in registers computes the same
+    products from the same split as the two-kernel path: equal up to the last alpha/beta FMA."""
+    m, n, k = shape
+    rng = np.random.default_rng(200 + m + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    A = _t(a) if la == "row" else _t(a.T).t()
+    B = _t(b) if lb == "row" else _t(b.T).t()
+    out = {}
+    for path in (1, 2):
+        tcec.set_option("path", path)
+        out[path] = tcec.sgemm(A, B).cpu().numpy()
+        tcec.device_status()
+    exact = cpu.gemm_f64(a, b)
+    assert np.array_equal(out[1].view(np.uint32), out[2].view(np.uint32))  # alpha = 1, beta = 0: same bits
+    assert cpu.errors(out[2], exact)["max_rel"] < 1e-6
+    c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    tcec.set_option("path", 2)
+    got = tcec.sgemm(A, B, _t(c0).clone(), alpha=1.5, beta=-0.5, policy="fp16_no_ec").cpu().numpy()
+    assert cpu.errors(got, 1.5 * exact - 0.5 * c0)["max_rel"] < 2e-3
+
+
+def test_fp32_tile_kernel_batched_and_fallback():
+    rng = np.random.default_rng(210)
+    a = rng.standard_normal((6, 256, 256)).astype(np.float32)
+    b = rng.standard_normal((6, 256, 256)).astype(np.float32)
+    tcec.set_option("path", 1)
+    want = tcec.sgemm_strided_batched(_t(a), _t(b))
+    tcec.set_option("path", 0)  # automatic: short-K batches take the FP32-tile kernel
+    got = tcec.sgemm_strided_batched(_t(a), _t(b))
+    tcec.device_status()
+    assert torch.equal(got, want)
+    # operands the TMA cannot address (leading dimension not a multiple of 4) fall back to panels
+    tcec.set_option("path", 2)
+    buf = torch.zeros(256, 259, device=DEV)
+    buf[:, :256] = _t(a[0])
+    odd = tcec.sgemm(buf[:, :256], _t(b[0]))
+    assert torch.equal(odd, want[0])
+    # tf32 policies always use panels
+    t32 = tcec.sgemm(_t(a[0]), _t(b[0]), policy="tf32_ec").cpu().numpy()
+    assert cpu.errors(t32, cpu.gemm_f64(a[0], b[0]))["max_rel"] < 1e-6
+    tcec.device_status()
 
 
 # ---------------------------------------------------------------- golden fixtures of the reference

@@ -10,6 +10,7 @@
 #include <utility>
 
 #include "../../include/tcec.h"
+#include "tcec_gemm_fused.cuh"
 #include "tcec_gemm_panels.cuh"
 #include "tcec_panels.cuh"
 
@@ -33,6 +34,7 @@ std::map<int, DeviceState> g_dev;
 int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
 int g_debug_flags = 0;
+int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
 unsigned long long* g_trace = nullptr;
 
 #define TCEC_CUDA(call)                        \
@@ -65,6 +67,10 @@ int get_device_state(DeviceState** out) {
     TCEC_CUDA((set_smem_attr<256, false, true>()));
     TCEC_CUDA((set_smem_attr<256, true, false>()));
     TCEC_CUDA((set_smem_attr<256, true, true>()));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   GemmFusedCfg<true>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   GemmFusedCfg<false>::SMEM_BYTES));
     if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return TCEC_ERR_ALLOC;
     TCEC_CUDA(cudaMemset(st.status, 0, sizeof(int)));
     st.attrs_done = true;
@@ -252,6 +258,81 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
 #undef TCEC_DISPATCH
 }
 
+// ---------------------------------------------------------------- FP32-tile (fused) path
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// Tensor map of one FP32 operand: `rows` along M (or N), `k` along K.  K-contiguous: element
+// (row, kk) at row*ld + kk, box 32 k x box_rows rows.  Otherwise (kk, row) at kk*ld + row, box
+// 32 rows x 32 k.  128-byte swizzle; out-of-range elements read as zero.
+bool encode_operand_map(CUtensorMap* map, const float* base, bool k_contiguous, int rows, int k, long long ld,
+                        long long batch_stride, int batch, int box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+      return false;
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const cuuint64_t inner = k_contiguous ? k : rows, outer = k_contiguous ? rows : k;
+  cuuint64_t dims[3] = {inner, outer, static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4,
+                           static_cast<cuuint64_t>(batch > 1 ? batch_stride : ld * static_cast<long long>(outer)) * 4};
+  cuuint32_t box[3] = {32u, static_cast<cuuint32_t>(k_contiguous ? box_rows : 32), 1u};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool tma_addressable(const float* base, long long ld, long long stride, int batch) {
+  return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ld % 4 == 0 && (batch <= 1 || stride % 4 == 0) &&
+         ld < (1ll << 36) && stride < (1ll << 36);
+}
+
+// Launches the FP32-tile kernel if the call qualifies; returns false (nothing launched) otherwise.
+bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const float* a, long long lda,
+               long long stride_a, const float* b, long long ldb, long long stride_b, float beta, float* c,
+               long long ldc, long long stride_c, int batch, int policy, const DeviceState* st,
+               cudaStream_t stream) {
+  if (policy_tf32(policy) || !a || !b || !c || n <= 128) return false;
+  // Worth it only where the GEMM is bound by DRAM traffic, which the split pass doubles: short K.
+  const bool wanted = g_path == 2 || (g_path == 0 && batch > 1 && k <= 512);
+  if (!wanted) return false;
+  if (!tma_addressable(a, lda, stride_a, batch) || !tma_addressable(b, ldb, stride_b, batch)) return false;
+  const bool a_kc = (la == TCEC_ROW_MAJOR), b_kc = (lb == TCEC_COL_MAJOR);
+  CUtensorMap map_a, map_b;
+  if (!encode_operand_map(&map_a, a, a_kc, m, k, lda, stride_a, batch, 128)) return false;
+  if (!encode_operand_map(&map_b, b, b_kc, n, k, ldb, stride_b, batch, 256)) return false;
+  GemmFusedParams fp{};
+  fp.M = m;
+  fp.N = n;
+  fp.K = k;
+  fp.batch = batch;
+  fp.nkb = (k + 31) / 32;
+  fp.tiles_m = (m + 127) / 128;
+  fp.tiles_n = (n + 255) / 256;
+  fp.promo = promote_blocks(k, policy, 32);
+  fp.a_k_contiguous = a_kc;
+  fp.b_k_contiguous = b_kc;
+  fp.alpha = alpha;
+  fp.beta = beta;
+  fp.c = c;
+  fp.ldc = ldc;
+  fp.c_batch_stride = stride_c;
+  fp.c_col_major = (lc == TCEC_COL_MAJOR);
+  fp.status = st->status;
+  const long long ntiles = static_cast<long long>(fp.tiles_m) * fp.tiles_n * batch;
+  const int grid = static_cast<int>(ntiles < st->sm_count ? ntiles : st->sm_count);
+  if (policy_ec(policy))
+    tcec_gemm_fused_kernel<true><<<grid, 384, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+  else
+    tcec_gemm_fused_kernel<false><<<grid, 384, GemmFusedCfg<false>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+  return true;
+}
+
 int scale_only(float beta, float* c, float* const* c_array, long long ldc, long long stride_c, int m,
                int n, int lc, int batch, cudaStream_t stream) {
   if (beta == 1.f) return TCEC_OK;
@@ -287,6 +368,12 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
   if (rc != TCEC_OK) return rc;
   if (k == 0 || alpha == 0.f) return scale_only(beta, c, c_array, ldc, stride_c, m, n, lc, batch, stream);
 
+  if (!a_array && !b_array && !c_array &&
+      try_fused(la, lb, lc, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc, stride_c, batch, policy,
+                st, stream)) {
+    TCEC_CUDA(cudaGetLastError());
+    return TCEC_OK;
+  }
   const Shape s = plan(m, n, k, policy);
   void* ws = nullptr;
   rc = get_workspace(st, stream, (s.a_bytes + s.b_bytes) * batch, &ws);
@@ -429,6 +516,11 @@ int tcec_set_option(const char* name, int value) {
   if (!strcmp(name, "tile_n")) {
     if (value != 0 && value != 128 && value != 256) return TCEC_ERR_INVALID_ARGUMENT;
     g_tile_n = value;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "path")) {
+    if (value < 0 || value > 2) return TCEC_ERR_INVALID_ARGUMENT;
+    g_path = value;
     return TCEC_OK;
   }
   if (!strcmp(name, "debug_flags")) {
