@@ -84,6 +84,21 @@ int tcec_sgemm_strided_batched(int layout_a, int layout_b, int layout_c, int m, 
                                void* stream);
 
 /*
+ * The same two calls in cuBLAS's convention, for host code that switches by renaming the call:
+ * column-major storage, transposition flags with cuBLAS's values (0 = CUBLAS_OP_N, 1 = _T,
+ * 2 = _C), alpha and beta by host pointer.  They stand in for the cublasSgemmBatched call the
+ * reference times its kernel against (test/tcec/batch_gemm.cu:619-621:
+ * cublasSgemmBatched(handle, CUBLAS_OP_T, CUBLAS_OP_N, m, n, k, &alpha, A, k, B, k, &beta, C, m, batch))
+ * and for cublasSgemm; the handle is replaced by (policy, stream).
+ */
+int tcec_sgemm_cublas(int transa, int transb, int m, int n, int k, const float* alpha, const float* a, int lda,
+                      const float* b, int ldb, const float* beta, float* c, int ldc, int policy, void* stream);
+int tcec_sgemm_batched_cublas(int transa, int transb, int m, int n, int k, const float* alpha,
+                              const float* const* a_array, int lda, const float* const* b_array, int ldb,
+                              const float* beta, float* const* c_array, int ldc, int batch, int policy,
+                              void* stream);
+
+/*
  * tcec_sgemm without any allocation.  This entry point has no counterpart in the reference.
  *
  * For callers that cannot call cudaMalloc when they need the product - a process whose memory

@@ -131,15 +131,17 @@ __device__ TCEC_FRAG(Use, Layout) neg(const TCEC_FRAG(Use, Layout) & frag) {
 namespace detail {
 // A / B operands: split on load.  Accumulators: copy (with error correction) or round through T
 // (without: the reference's accumulator load does the same, tcec/detail/no_cor.hpp:165-166).
-template <class MemLayout, class Use, class Layout, TCEC_TPARAMS, class MEM_T>
-__device__ void load_impl(TCEC_FRAG(Use, Layout) & frag, const MEM_T* const ptr, const unsigned ldm,
-                          const float mul, const bool use_mul) {
+// `get(index)` returns the FP32 value at a linear memory index, so the same code serves plain
+// FP32 arrays and the real / imaginary parts of interleaved complex arrays.
+template <class MemLayout, class Use, class Layout, TCEC_TPARAMS, class Get>
+__device__ void load_with(TCEC_FRAG(Use, Layout) & frag, Get get, const unsigned ldm, const float mul,
+                          const bool use_mul) {
   using F = TCEC_FRAG(Use, Layout);
   using tile_t = typename F::sub_frag_t;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
     for (int bm = 0; bm < F::num_sub_frag_m; bm++)
       for (int bn = 0; bn < F::num_sub_frag_n; bn++) {
-        float v = static_cast<float>(ptr[mem_index<MemLayout>(i + bm * tile_t::rows, j + bn * tile_t::cols, ldm)]);
+        float v = get(mem_index<MemLayout>(i + bm * tile_t::rows, j + bn * tile_t::cols, ldm));
         if (use_mul) v *= mul;
         const int f = bm + F::num_sub_frag_m * bn;
         if constexpr (std::is_same<Use, nvcuda::wmma::accumulator>::value) {
@@ -158,6 +160,11 @@ __device__ void load_impl(TCEC_FRAG(Use, Layout) & frag, const MEM_T* const ptr,
         }
       }
   });
+}
+template <class MemLayout, class Use, class Layout, TCEC_TPARAMS, class MEM_T>
+__device__ void load_impl(TCEC_FRAG(Use, Layout) & frag, const MEM_T* const ptr, const unsigned ldm,
+                          const float mul, const bool use_mul) {
+  load_with<MemLayout>(frag, [ptr](unsigned idx) { return static_cast<float>(ptr[idx]); }, ldm, mul, use_mul);
 }
 }  // namespace detail
 
@@ -202,9 +209,9 @@ __device__ void load_matrix_sync_with_mul(TCEC_FRAG(Use, Layout) & frag, const M
 
 // ---------------------------------------------------------------- stores (fold)
 namespace detail {
-template <class MemLayout, TCEC_TPARAMS, class MEM_T>
-__device__ void store_impl(MEM_T* const ptr, const TCEC_FRAG(nvcuda::wmma::accumulator, void) & frag,
-                           const unsigned ldm, const float mul, const bool use_mul) {
+template <class MemLayout, TCEC_TPARAMS, class Put>
+__device__ void store_with(Put put, const TCEC_FRAG(nvcuda::wmma::accumulator, void) & frag, const unsigned ldm,
+                           const float mul, const bool use_mul) {
   using F = TCEC_FRAG(nvcuda::wmma::accumulator, void);
   using tile_t = typename F::sub_frag_t;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
@@ -214,9 +221,14 @@ __device__ void store_impl(MEM_T* const ptr, const TCEC_FRAG(nvcuda::wmma::accum
         float v = frag.sub_frag[f].x[r];
         if constexpr (F::error_corrected) v = v + frag.sub_d_frag[f].x[r] * residual_scale<T>::down;
         if (use_mul) v *= mul;
-        ptr[mem_index<MemLayout>(i + bm * tile_t::rows, j + bn * tile_t::cols, ldm)] = static_cast<MEM_T>(v);
+        put(mem_index<MemLayout>(i + bm * tile_t::rows, j + bn * tile_t::cols, ldm), v);
       }
   });
+}
+template <class MemLayout, TCEC_TPARAMS, class MEM_T>
+__device__ void store_impl(MEM_T* const ptr, const TCEC_FRAG(nvcuda::wmma::accumulator, void) & frag,
+                           const unsigned ldm, const float mul, const bool use_mul) {
+  store_with<MemLayout>([ptr](unsigned idx, float v) { ptr[idx] = static_cast<MEM_T>(v); }, frag, ldm, mul, use_mul);
 }
 }  // namespace detail
 

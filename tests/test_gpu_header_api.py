@@ -188,6 +188,15 @@ def test_reference_mma_test_program_passes_on_these_headers():
     assert m.group(1) == m.group(2) and int(m.group(2)) >= 300, m.group(0)
 
 
+def test_reference_complex_mma_test_program_passes_on_these_headers():
+    """test/tcec/mma_complex.cu of the reference (fragment_complex, four real products per
+    complex product), compiled unchanged against this repository's complex.hpp."""
+    text = _run_reference_test_binary("reftest_mma_complex.newhdr")
+    m = re.search(r"passed\s*:\s*(\d+)\s*/\s*(\d+)", text)
+    assert m, text[-500:]
+    assert m.group(1) == m.group(2) and int(m.group(2)) >= 100, m.group(0)
+
+
 def test_reference_matvec_test_program_passes_on_these_headers():
     text = _run_reference_test_binary("reftest_matvec.newhdr")
     assert "FAILED" not in text and text.count("PASSED") >= 4, text[-800:]

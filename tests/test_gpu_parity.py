@@ -296,6 +296,45 @@ def test_packed_entry_points_match_plain_call():
     tcec.device_status()
 
 
+# ---------------------------------------------------------------- cuBLAS-convention entry points
+def test_cublas_convention_calls():
+    """Column-major storage with transposition flags, exactly the argument list of the
+    cublasSgemmBatched call the reference benchmarks against (OP_T, OP_N, lda = ldb = k, ldc = m)."""
+    import ctypes
+
+    lib = tcec.load()
+    rng = np.random.default_rng(60)
+    m, n, k, batch = 200, 130, 96, 3
+    a = rng.standard_normal((batch, m, k)).astype(np.float32)  # logical A (m x k)
+    b = rng.standard_normal((batch, k, n)).astype(np.float32)  # logical B (k x n)
+    c0 = rng.standard_normal((batch, m, n)).astype(np.float32)
+    alpha, beta = ctypes.c_float(1.25), ctypes.c_float(-0.5)
+    for ta in (0, 1):
+        for tb in (0, 1):
+            # N: column-major storage of the logical matrix; T: column-major storage of its transpose
+            a_mem = _t(a.transpose(0, 2, 1)) if ta == 0 else _t(a)   # (k, m) rows = col-major m x k ; T: rows of A
+            b_mem = _t(b.transpose(0, 2, 1)) if tb == 0 else _t(b)
+            lda = m if ta == 0 else k
+            ldb = k if tb == 0 else n
+            c_mem = _t(c0.transpose(0, 2, 1)).clone()                # column-major m x n, ldc = m
+            st = lib.tcec_sgemm_cublas(ta, tb, m, n, k, ctypes.byref(alpha), a_mem[0].data_ptr(), lda,
+                                       b_mem[0].data_ptr(), ldb, ctypes.byref(beta), c_mem[0].data_ptr(), m, 0, None)
+            assert st == tcec.OK
+            ptrs = [torch.tensor([x[i].data_ptr() for i in range(1, batch)], dtype=torch.int64, device=DEV)
+                    for x in (a_mem, b_mem, c_mem)]
+            st = lib.tcec_sgemm_batched_cublas(ta, tb, m, n, k, ctypes.byref(alpha), ptrs[0].data_ptr(), lda,
+                                               ptrs[1].data_ptr(), ldb, ctypes.byref(beta), ptrs[2].data_ptr(), m,
+                                               batch - 1, 0, None)
+            assert st == tcec.OK
+            tcec.device_status()
+            got = c_mem.cpu().numpy().transpose(0, 2, 1)
+            for i in range(batch):
+                want = 1.25 * cpu.gemm_f64(a[i], b[i]) - 0.5 * c0[i]
+                assert cpu.errors(got[i], want)["max_rel"] < 1e-6, (ta, tb, i)
+    assert lib.tcec_sgemm_cublas(5, 0, 4, 4, 4, ctypes.byref(alpha), None, 4, None, 4, ctypes.byref(beta), None, 4,
+                                 0, None) == tcec.ERR_INVALID_ARGUMENT
+
+
 # ---------------------------------------------------------------- live reference comparator
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref was not built")
 @pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec"])

@@ -477,6 +477,36 @@ int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void
   return TCEC_OK;
 }
 
+// cuBLAS calling convention: column-major storage, transposition flags (0 = N, 1 = T, 2 = C),
+// alpha and beta by host pointer.  op(A) is m x k: stored column-major m x k (N) or as its
+// transpose k x m (T), which is a row-major m x k matrix with the same leading dimension.
+static int cublas_layout(int trans, int* layout) {
+  if (trans == 0) *layout = TCEC_COL_MAJOR;
+  else if (trans == 1 || trans == 2) *layout = TCEC_ROW_MAJOR;
+  else return TCEC_ERR_INVALID_ARGUMENT;
+  return TCEC_OK;
+}
+
+int tcec_sgemm_cublas(int transa, int transb, int m, int n, int k, const float* alpha, const float* a, int lda,
+                      const float* b, int ldb, const float* beta, float* c, int ldc, int policy, void* stream) {
+  int la, lb;
+  if (!alpha || !beta || cublas_layout(transa, &la) != TCEC_OK || cublas_layout(transb, &lb) != TCEC_OK)
+    return TCEC_ERR_INVALID_ARGUMENT;
+  return gemm_impl(la, lb, TCEC_COL_MAJOR, m, n, k, *alpha, a, nullptr, lda, 0, b, nullptr, ldb, 0, *beta, c,
+                   nullptr, ldc, 0, 1, policy, stream);
+}
+
+int tcec_sgemm_batched_cublas(int transa, int transb, int m, int n, int k, const float* alpha,
+                              const float* const* a_array, int lda, const float* const* b_array, int ldb,
+                              const float* beta, float* const* c_array, int ldc, int batch, int policy,
+                              void* stream) {
+  int la, lb;
+  if (!alpha || !beta || cublas_layout(transa, &la) != TCEC_OK || cublas_layout(transb, &lb) != TCEC_OK)
+    return TCEC_ERR_INVALID_ARGUMENT;
+  return gemm_impl(la, lb, TCEC_COL_MAJOR, m, n, k, *alpha, nullptr, a_array, lda, 0, nullptr, b_array, ldb, 0,
+                   *beta, nullptr, c_array, ldc, 0, batch, policy, stream);
+}
+
 int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, void* stream) {
   if (policy < 0 || policy > 3) return TCEC_ERR_INVALID_ARGUMENT;
   if (count == 0) return TCEC_OK;

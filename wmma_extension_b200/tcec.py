@@ -33,6 +33,8 @@ EXPORTED_SYMBOLS = (
     "tcec_pack_b",
     "tcec_sgemm_packed",
     "tcec_split",
+    "tcec_sgemm_cublas",
+    "tcec_sgemm_batched_cublas",
     "tcec_sgemm_static",
     "tcec_static_scratch_bytes",
     "tcec_static_status",
@@ -82,6 +84,11 @@ def load() -> ctypes.CDLL:
     lib.tcec_pack_b.restype = i
     lib.tcec_sgemm_packed.argtypes = [i, i, i, i, f, p, p, f, p, ll, i, p]
     lib.tcec_sgemm_packed.restype = i
+    fp = ctypes.POINTER(ctypes.c_float)
+    lib.tcec_sgemm_cublas.argtypes = [i, i, i, i, i, fp, p, i, p, i, fp, p, i, i, p]
+    lib.tcec_sgemm_cublas.restype = i
+    lib.tcec_sgemm_batched_cublas.argtypes = [i, i, i, i, i, fp, p, i, p, i, fp, p, i, i, i, p]
+    lib.tcec_sgemm_batched_cublas.restype = i
     lib.tcec_sgemm_static.argtypes = [i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, p]
     lib.tcec_sgemm_static.restype = i
     lib.tcec_static_scratch_bytes.argtypes = []
