@@ -33,10 +33,12 @@ def _defaults():
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
+    tcec.set_option("cta_pair", 0)
     yield
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
+    tcec.set_option("cta_pair", 0)
 
 
 # ---------------------------------------------------------------- split (bit-exact)
@@ -220,6 +222,34 @@ def test_fp32_tile_kernel_batched_and_fallback():
     t32 = tcec.sgemm(_t(a[0]), _t(b[0]), policy="tf32_ec").cpu().numpy()
     assert cpu.errors(t32, cpu.gemm_f64(a[0], b[0]))["max_rel"] < 1e-6
     tcec.device_status()
+
+
+# ---------------------------------------------------------------- CTA-pair kernel (cta_group::2)
+@pytest.mark.parametrize("shape,policy", [((256, 256, 32), "fp16_ec"), ((300, 300, 100), "fp16_ec"),
+                                          ((129, 257, 33), "tf32_ec"), ((1000, 700, 300), "fp16_no_ec"),
+                                          ((1024, 1024, 2048), "fp16_ec")])
+def test_cta_pair_kernel_is_bit_identical(shape, policy):
+    """Two SMs sharing a 256 x 256 tile compute every output row exactly as one SM does."""
+    m, n, k = shape
+    rng = np.random.default_rng(300 + m + k)
+    a = _t(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = _t(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    tcec.set_option("path", 1)
+    out = {}
+    for pair in (0, 1):
+        tcec.set_option("cta_pair", pair)
+        out[pair] = tcec.sgemm(a, b, policy=policy)
+        tcec.device_status()
+    assert torch.equal(out[0], out[1])
+    # batched, with a tile row that only the leader CTA has rows in (m = 150 < 256)
+    ab = _t(rng.standard_normal((5, 150, 96)).astype(np.float32))
+    bb = _t(rng.standard_normal((5, 96, 260)).astype(np.float32))
+    tcec.set_option("cta_pair", 0)
+    want = tcec.sgemm_strided_batched(ab, bb, policy=policy)
+    tcec.set_option("cta_pair", 1)
+    got = tcec.sgemm_strided_batched(ab, bb, policy=policy)
+    tcec.device_status()
+    assert torch.equal(got, want)
 
 
 # ---------------------------------------------------------------- golden fixtures of the reference

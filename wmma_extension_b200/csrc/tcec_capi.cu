@@ -12,6 +12,7 @@
 #include "../../include/tcec.h"
 #include "tcec_gemm_fused.cuh"
 #include "tcec_gemm_panels.cuh"
+#include "tcec_gemm_panels_pair.cuh"
 #include "tcec_panels.cuh"
 
 using namespace tcec_sm100;
@@ -34,6 +35,7 @@ std::map<int, DeviceState> g_dev;
 int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
 int g_debug_flags = 0;
+int g_cta_pair = 0;  // 0: off, 1: CTA-pair kernel for 256-wide tiles when the problem is large enough
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
 unsigned long long* g_trace = nullptr;
 
@@ -71,6 +73,14 @@ int get_device_state(DeviceState** out) {
                                    GemmFusedCfg<true>::SMEM_BYTES));
     TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    GemmFusedCfg<false>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, true>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, false>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, true>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, false>::SMEM_BYTES));
     if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return TCEC_ERR_ALLOC;
     TCEC_CUDA(cudaMemset(st.status, 0, sizeof(int)));
     st.attrs_done = true;
@@ -240,6 +250,22 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
   gp.debug_flags = g_debug_flags;
   gp.trace = g_trace;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
+  if (g_cta_pair && s.tile_n == 256 && m > 128) {
+    // CTA pairs: 256 x 256 tiles, grid of up to sm_count/2 clusters of two CTAs
+    gp.tiles_m = (m + 255) / 256;
+    const long long npair_tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
+    const int max_pairs = st->sm_count / 2;
+    const int grid = 2 * static_cast<int>(npair_tiles < max_pairs ? npair_tiles : max_pairs);
+    if (tf32 && ec)
+      tcec_gemm_panels_pair_kernel<true, true><<<grid, 384, GemmPairCfg<true, true>::SMEM_BYTES, stream>>>(gp);
+    else if (tf32)
+      tcec_gemm_panels_pair_kernel<true, false><<<grid, 384, GemmPairCfg<true, false>::SMEM_BYTES, stream>>>(gp);
+    else if (ec)
+      tcec_gemm_panels_pair_kernel<false, true><<<grid, 384, GemmPairCfg<false, true>::SMEM_BYTES, stream>>>(gp);
+    else
+      tcec_gemm_panels_pair_kernel<false, false><<<grid, 384, GemmPairCfg<false, false>::SMEM_BYTES, stream>>>(gp);
+    return;
+  }
 #define TCEC_DISPATCH(T, E)                                      \
   do {                                                           \
     if (s.tile_n == 256)                                         \
@@ -546,6 +572,11 @@ int tcec_set_option(const char* name, int value) {
   if (!strcmp(name, "tile_n")) {
     if (value != 0 && value != 128 && value != 256) return TCEC_ERR_INVALID_ARGUMENT;
     g_tile_n = value;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "cta_pair")) {
+    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
+    g_cta_pair = value;
     return TCEC_OK;
   }
   if (!strcmp(name, "path")) {

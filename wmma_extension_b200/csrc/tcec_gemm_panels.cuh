@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int left_in_chunk = 0;  // k blocks still to issue in the current chunk
         for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, (p.debug_flags & 8) ? 160u : ((p.debug_flags & 16) ? 0u : 32u))) {
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32u)) {
             ok = false;
             break;
           }
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
           for (int kb = 0; kb < p.nkb; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, (p.debug_flags & 8) ? 160u : ((p.debug_flags & 16) ? 0u : 32u))) {
+            if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32u)) {
               ok = false;
               break;
             }

@@ -1,0 +1,366 @@
+// The panel GEMM on CTA pairs (tcgen05 cta_group::2): two SMs share one 256 x 256 output tile.
+//
+// Same arithmetic, panel format, roles and TMEM layout as tcec_gemm_panels.cuh.  What changes:
+// each CTA of a pair loads the A panels of its own 128 rows and only its half of the B panels
+// (128 of the tile's 256 N rows), and the leader CTA issues every MMA for both SMs
+// (M = 256, N = 256, K = 16): per SM and K block 32 KB instead of 48 KB come through L2 and
+// 48 KB instead of 72 KB of operands are read from shared memory, which matters because the
+// kernel runs at the power cap, and the ring holds 6 stages instead of 4.
+//
+// Pair protocol (rank 0 = leader, rank 1 = peer):
+//   full[s]   leader's barrier: its own copies' bytes + one remote arrive by the peer's relay
+//             thread (peer warp 1), which waits on the peer's local full[s] first
+//   empty[s]  committed by the leader's two MMA threads to BOTH CTAs (multicast commit)
+//   main_full / corr_full   likewise committed to both CTAs; each CTA drains its own TMEM
+//   main_free / corr_free   leader's barriers: 8 local epilogue warps + 8 remote arrives
+// Both CTAs meet at a cluster barrier after set-up and before exit.
+#pragma once
+#include "sm100_ptx.cuh"
+#include "tcec_gemm_panels.cuh"
+
+namespace tcec_sm100 {
+
+template <bool kTf32, bool kEc>
+struct GemmPairCfg {
+  static constexpr int NP = kEc ? 2 : 1;
+  static constexpr int A_BYTES = kPanelBytes * NP;   // this CTA's 128 rows of A: hi (+ lo)
+  static constexpr int B_BYTES = kPanelBytes * NP;   // this CTA's 128 of the tile's 256 N rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NST_RAW = (200 * 1024) / STAGE_BYTES;
+  static constexpr int NST = NST_RAW > 8 ? 8 : NST_RAW;
+  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + 1024;
+  static constexpr int TMEM_COLS = kEc ? 512 : 256;
+  static constexpr int THREADS = 384;
+  static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
+};
+
+// p.tiles_m counts 256-row pair tiles here.
+template <bool kTf32, bool kEc>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
+    tcec_gemm_panels_pair_kernel(const GemmPanelParams p) {
+  using Cfg = GemmPairCfg<kTf32, kEc>;
+  constexpr int NST = Cfg::NST, BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[NST], bar_empty[NST];
+  __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = (rank == 0);
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int ntiles = p.tiles_m * p.tiles_n * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), leader ? 2 : 1);  // leader: own producer + the peer's relay
+      mbar_init(smem_u32(&bar_empty[s]), kEc ? 2 : 1);
+    }
+    mbar_init(smem_u32(&bar_main_full), 1);
+    mbar_init(smem_u32(&bar_main_free), 16);  // used in the leader only: 8 warps of each CTA
+    mbar_init(smem_u32(&bar_corr_full), 1);
+    mbar_init(smem_u32(&bar_corr_free), 16);
+    mbar_init(smem_u32(&bar_drain[0]), 1);
+    mbar_init(smem_u32(&bar_drain[1]), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_base_s), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_main = tmem_base_s;
+  const uint32_t tmem_corr = tmem_base_s + BN;
+  volatile uint32_t* abortp = &abort_flag;
+
+  if (warp < 4) {
+    if (warp == 0) {
+      // ---------------------------------------------------------- producer (each CTA, own panels)
+      if (lane == 0) {
+        uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0;
+        bool ok = true;
+        for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+          const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+          const uint8_t* pa = p.panels_a + tc.b * p.panels_a_batch_stride +
+                              static_cast<size_t>(tc.mt * 2 + rank) * p.nkb * Cfg::A_BYTES;
+          const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
+                              static_cast<size_t>(tc.nt * 2 + rank) * p.nkb * Cfg::B_BYTES;
+          for (int kb = 0; kb < p.nkb; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp, 128)) {
+              ok = false;
+              break;
+            }
+            const uint32_t full = smem_u32(&bar_full[s]);
+            const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
+            mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+            armed |= 1u << s;
+            armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+            bulk_load(dst, pa + static_cast<size_t>(kb) * Cfg::A_BYTES, Cfg::A_BYTES, full);
+            bulk_load(dst + Cfg::A_BYTES, pb + static_cast<size_t>(kb) * Cfg::B_BYTES, Cfg::B_BYTES, full);
+            if (++s == static_cast<uint32_t>(NST)) {
+              s = 0;
+              ph ^= 1;
+            }
+          }
+        }
+        if (!ok) {
+          abort_flag = 1;
+          atomicCAS(p.status, 0, kErrProducerWait);
+          for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
+            if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_full[q]), (armed_parity >> q) & 1);
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        if (!leader) {
+          // -------------------------------------------------------- peer: relay "my stage landed"
+          uint32_t s = 0, ph = 0;
+          bool ok = true;
+          for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+            for (int kb = 0; kb < p.nkb; ++kb) {
+              if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
+                ok = false;
+                break;
+              }
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bar_full[s]), 0));
+              if (++s == static_cast<uint32_t>(NST)) {
+                s = 0;
+                ph ^= 1;
+              }
+            }
+          }
+          if (!ok) {
+            abort_flag = 1;
+            atomicCAS(p.status, 0, kErrMmaWait);
+          }
+        } else {
+          // -------------------------------------------------------- leader: main products
+          const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
+          const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+          constexpr uint32_t kBHi = Cfg::A_BYTES >> 4;
+          const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
+          uint32_t s = 0, ph = 0, chunk = 0;
+          bool ok = true;
+          for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+            int left_in_chunk = 0;
+            for (int kb = 0; kb < p.nkb; ++kb) {
+              if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
+                ok = false;
+                break;
+              }
+              const bool first_in_chunk = (left_in_chunk == 0);
+              if (first_in_chunk) {
+                const int rest = p.nkb - kb;
+                left_in_chunk = (p.promo && p.promo < rest) ? p.promo : rest;
+                if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp, 0)) {
+                  ok = false;
+                  break;
+                }
+              }
+              tc_fence_after();
+              const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+#pragma unroll
+              for (uint32_t j = 0; j < 2; ++j)
+                umma_ss_pair<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
+                                    (first_in_chunk && j == 0) ? 0u : 1u);
+              if (--left_in_chunk == 0) {
+                umma_commit_pair(smem_u32(&bar_main_full));
+                ++chunk;
+              }
+              umma_commit_pair(smem_u32(&bar_empty[s]));
+              if (++s == static_cast<uint32_t>(NST)) {
+                s = 0;
+                ph ^= 1;
+              }
+            }
+          }
+          if (!ok) {
+            abort_flag = 1;
+            atomicCAS(p.status, 0, kErrMmaWait);
+            umma_commit_pair(smem_u32(&bar_drain[0]));
+            mbar_wait_plain(smem_u32(&bar_drain[0]), 0);
+          }
+        }
+      }
+    } else if (warp == 2) {
+      // ---------------------------------------------------------- leader: correction products
+      if constexpr (kEc) {
+        if (lane == 0 && leader) {
+          const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
+          const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+          constexpr uint32_t kALo = kPanelBytes >> 4, kBHi = Cfg::A_BYTES >> 4,
+                             kBLo = (Cfg::A_BYTES + kPanelBytes) >> 4;
+          const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
+          uint32_t s = 0, ph = 0, tcount = 0;
+          bool ok = true;
+          for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
+            for (int kb = 0; kb < p.nkb; ++kb) {
+              if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
+                ok = false;
+                break;
+              }
+              if (kb == 0) {
+                if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
+                  ok = false;
+                  break;
+                }
+              }
+              tc_fence_after();
+              const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+#pragma unroll
+              for (uint32_t j = 0; j < 2; ++j)
+                umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
+                                    (kb == 0 && j == 0) ? 0u : 1u);
+#pragma unroll
+              for (uint32_t j = 0; j < 2; ++j)
+                umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
+              umma_commit_pair(smem_u32(&bar_empty[s]));
+              if (++s == static_cast<uint32_t>(NST)) {
+                s = 0;
+                ph ^= 1;
+              }
+            }
+            if (!ok) break;
+            umma_commit_pair(smem_u32(&bar_corr_full));
+          }
+          if (!ok) {
+            abort_flag = 1;
+            atomicCAS(p.status, 0, kErrMmaWait);
+            umma_commit_pair(smem_u32(&bar_drain[1]));
+            mbar_wait_plain(smem_u32(&bar_drain[1]), 0);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (each CTA, its 128 rows)
+    const int ew = warp - 4;
+    const int q = warp & 3;
+    const int colbase = (ew >> 2) * 128;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float corr_scale = kTf32 ? 1.0f : (1.0f / 2048.0f);
+    const bool vec_store = !p.c_col_major && (p.ldc % 4 == 0);
+    const uint32_t main_free_leader = map_to_cta(smem_u32(&bar_main_free), 0);
+    const uint32_t corr_free_leader = map_to_cta(smem_u32(&bar_corr_free), 0);
+    uint32_t chunk = 0, tcount = 0;
+    bool ok = true;
+    for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
+      const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+      const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
+      float acc[128];
+      for (int c = 0; c < nchunks; ++c, ++chunk) {
+        if (!mbar_wait_warp(smem_u32(&bar_main_full), chunk & 1, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
+          tmem_ld_wait();
+          if (c == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(main_free_leader);
+      }
+      if (!ok) break;
+      if constexpr (kEc) {
+        if (!mbar_wait_warp(smem_u32(&bar_corr_full), tcount & 1, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
+      const int row = tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32 + lane;
+      const int col0 = tc.nt * BN + colbase;
+      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+      if constexpr (kEc) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * corr_scale;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(corr_free_leader);
+      }
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        if (row < p.M) {
+          if (!p.c_col_major) {
+            float* crow = cbase + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const int col = col0 + cc * 32 + i;
+              if (vec_ok && col + 3 < p.N) {
+                float4 o;
+                o.x = p.alpha * acc[cc * 32 + i + 0];
+                o.y = p.alpha * acc[cc * 32 + i + 1];
+                o.z = p.alpha * acc[cc * 32 + i + 2];
+                o.w = p.alpha * acc[cc * 32 + i + 3];
+                if (p.beta != 0.f) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + col);
+                  o.x += p.beta * old.x;
+                  o.y += p.beta * old.y;
+                  o.z += p.beta * old.z;
+                  o.w += p.beta * old.w;
+                }
+                *reinterpret_cast<float4*>(crow + col) = o;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (col + e < p.N) {
+                    float o = p.alpha * acc[cc * 32 + i + e];
+                    if (p.beta != 0.f) o += p.beta * crow[col + e];
+                    crow[col + e] = o;
+                  }
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = col0 + cc * 32 + i;
+              if (col < p.N) {
+                float* dst = cbase + static_cast<long long>(col) * p.ldc + row;
+                float o = p.alpha * acc[cc * 32 + i];
+                if (p.beta != 0.f) o += p.beta * *dst;
+                *dst = o;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicCAS(p.status, 0, kErrEpilogueWait);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still signal it or read its operands
+  if (warp == 1) tmem_dealloc_pair(tmem_base_s, Cfg::TMEM_COLS);
+}
+
+}  // namespace tcec_sm100
