@@ -170,8 +170,9 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *   "tile_n"     0 = automatic, 128 or 256.
  *   "cta_pair"   1 = run 256-wide tiles on pairs of SMs (tcgen05 cta_group::2: 256 x 256 tiles,
  *                each SM loads its rows of A and half of B).  Bit-identical results; off by
- *                default because it measured slower than one SM per tile (412 vs 456 TFLOP/s
- *                at 8192^3).
+ *                default: 4 % faster than one SM per tile at 4096^3 (389 vs 373 TFLOP/s) but it
+ *                draws more power, and at the board's power cap it is slower (16384^3: 360 vs
+ *                400 TFLOP/s, both at 990 W).
  *   "path"       0 = automatic; 1 = always split the operands into panels first, then multiply
  *                (two kernels; the faster one whenever the tensor pipe is the limit); 2 = use
  *                the single kernel that TMA-loads FP32 tiles and splits them in registers

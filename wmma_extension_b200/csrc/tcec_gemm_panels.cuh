@@ -44,7 +44,7 @@ struct GemmPanelParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;             // device word; non-zero after a wait ran out
-  int debug_flags;         // timing experiments only: bit 0 = reuse resident stages (results invalid)
+  int debug_flags;         // timing experiments only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
   unsigned long long* trace;  // optional: CTA 0 writes clock64() at hand-off points (6 roles x 4096 slots)
 };
 
@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
           }
           tc_fence_after();
           const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+          if (!(p.debug_flags & 2))
 #pragma unroll
           for (uint32_t j = 0; j < 2; ++j)
             umma_ss<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
             trace_mark(p, 4, cit++);
             tc_fence_after();
             const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+            if (!(p.debug_flags & 2)) {
 #pragma unroll
             for (uint32_t j = 0; j < 2; ++j)
               umma_ss<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
@@ -262,6 +264,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
 #pragma unroll
             for (uint32_t j = 0; j < 2; ++j)
               umma_ss<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
+            }
             umma_commit(smem_u32(&bar_empty[s]));
             if (++s == static_cast<uint32_t>(NST)) {
               s = 0;

@@ -4,12 +4,16 @@
 // each CTA of a pair loads the A panels of its own 128 rows and only its half of the B panels
 // (128 of the tile's 256 N rows), and the leader CTA issues every MMA for both SMs
 // (M = 256, N = 256, K = 16): per SM and K block 32 KB instead of 48 KB come through L2 and
-// 48 KB instead of 72 KB of operands are read from shared memory, which matters because the
-// kernel runs at the power cap, and the ring holds 6 stages instead of 4.
+// 48 KB instead of 72 KB of operands are read from shared memory, and the ring holds 6 stages
+// instead of 4.  Measured: a little faster than one SM per tile while the clocks are high
+// (4096^3), but it draws more power per product, so it is slower once the board sits at its
+// power cap (16384^3); the host library therefore keeps it behind an option.
 //
 // Pair protocol (rank 0 = leader, rank 1 = peer):
 //   full[s]   leader's barrier: its own copies' bytes + one remote arrive by the peer's relay
-//             thread (peer warp 1), which waits on the peer's local full[s] first
+//             thread (peer warp 1), which waits on the peer's local full[s] first.  The remote
+//             arrive has CTA scope: with cluster-scope release every arrive waited for the
+//             SM's copies in flight and the ring degenerated to one stage at a time.
 //   empty[s]  committed by the leader's two MMA threads to BOTH CTAs (multicast commit)
 //   main_full / corr_full   likewise committed to both CTAs; each CTA drains its own TMEM
 //   main_free / corr_free   leader's barriers: 8 local epilogue warps + 8 remote arrives
@@ -33,6 +37,10 @@ struct GemmPairCfg {
   static constexpr int THREADS = 384;
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
 };
+
+__device__ __forceinline__ void pair_trace(const GemmPanelParams& p, int role, uint32_t idx) {
+  if (p.trace && (blockIdx.x >> 1) == 0 && idx < 4096) p.trace[role * 4096 + idx] = clock64();
+}
 
 // p.tiles_m counts 256-row pair tiles here.
 template <bool kTf32, bool kEc>
@@ -83,7 +91,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     if (warp == 0) {
       // ---------------------------------------------------------- producer (each CTA, own panels)
       if (lane == 0) {
-        uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0;
+        uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0, it = 0;
         bool ok = true;
         for (int tile = pair; tile < ntiles && ok; tile += npairs) {
           const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
@@ -91,10 +99,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
                               static_cast<size_t>(tc.mt * 2 + rank) * p.nkb * Cfg::A_BYTES;
           const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
                               static_cast<size_t>(tc.nt * 2 + rank) * p.nkb * Cfg::B_BYTES;
-          for (int kb = 0; kb < p.nkb; ++kb) {
+          for (int kb = 0; kb < p.nkb; ++kb, ++it) {
             if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp, 128)) {
               ok = false;
               break;
+            }
+            pair_trace(p, leader ? 2 : 3, it);
+            if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {  // timing experiment: no loads
+              mbar_arrive(smem_u32(&bar_full[s]));
+              if (++s == static_cast<uint32_t>(NST)) {
+                s = 0;
+                ph ^= 1;
+              }
+              continue;
             }
             const uint32_t full = smem_u32(&bar_full[s]);
             const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
@@ -120,14 +137,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       if (lane == 0) {
         if (!leader) {
           // -------------------------------------------------------- peer: relay "my stage landed"
-          uint32_t s = 0, ph = 0;
+          uint32_t s = 0, ph = 0, it = 0;
           bool ok = true;
           for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-            for (int kb = 0; kb < p.nkb; ++kb) {
+            for (int kb = 0; kb < p.nkb; ++kb, ++it) {
               if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
                 ok = false;
                 break;
               }
+              pair_trace(p, 1, it);
               mbar_arrive_cluster(map_to_cta(smem_u32(&bar_full[s]), 0));
               if (++s == static_cast<uint32_t>(NST)) {
                 s = 0;
@@ -145,15 +163,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
           constexpr uint32_t kBHi = Cfg::A_BYTES >> 4;
           const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-          uint32_t s = 0, ph = 0, chunk = 0;
+          uint32_t s = 0, ph = 0, chunk = 0, it = 0;
           bool ok = true;
           for (int tile = pair; tile < ntiles && ok; tile += npairs) {
             int left_in_chunk = 0;
-            for (int kb = 0; kb < p.nkb; ++kb) {
+            for (int kb = 0; kb < p.nkb; ++kb, ++it) {
               if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
                 ok = false;
                 break;
               }
+              pair_trace(p, 0, it);
               const bool first_in_chunk = (left_in_chunk == 0);
               if (first_in_chunk) {
                 const int rest = p.nkb - kb;
@@ -165,6 +184,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
               }
               tc_fence_after();
               const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+              if (!(p.debug_flags & 2))  // timing experiment: no MMAs
 #pragma unroll
               for (uint32_t j = 0; j < 2; ++j)
                 umma_ss_pair<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
@@ -174,6 +194,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
                 ++chunk;
               }
               umma_commit_pair(smem_u32(&bar_empty[s]));
+              pair_trace(p, 5, it);
               if (++s == static_cast<uint32_t>(NST)) {
                 s = 0;
                 ph ^= 1;
@@ -197,14 +218,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           constexpr uint32_t kALo = kPanelBytes >> 4, kBHi = Cfg::A_BYTES >> 4,
                              kBLo = (Cfg::A_BYTES + kPanelBytes) >> 4;
           const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-          uint32_t s = 0, ph = 0, tcount = 0;
+          uint32_t s = 0, ph = 0, tcount = 0, it = 0;
           bool ok = true;
           for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
-            for (int kb = 0; kb < p.nkb; ++kb) {
+            for (int kb = 0; kb < p.nkb; ++kb, ++it) {
               if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
                 ok = false;
                 break;
               }
+              pair_trace(p, 4, it);
               if (kb == 0) {
                 if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
                   ok = false;
@@ -213,6 +235,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
               }
               tc_fence_after();
               const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
+              if (!(p.debug_flags & 2)) {
 #pragma unroll
               for (uint32_t j = 0; j < 2; ++j)
                 umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
@@ -220,6 +243,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
 #pragma unroll
               for (uint32_t j = 0; j < 2; ++j)
                 umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
+              }
               umma_commit_pair(smem_u32(&bar_empty[s]));
               if (++s == static_cast<uint32_t>(NST)) {
                 s = 0;
