@@ -150,6 +150,21 @@ int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void
                       const void* b_packed, float beta, float* c, long long ldc, int policy, void* stream);
 
 /*
+ * Complex GEMM on interleaved (re, im) float pairs: C = alpha * A * B + beta * C.
+ * `a`, `b`, `c` point at the real part of the first element; lda, ldb, ldc count
+ * complex elements; alpha and beta are two floats each (re, im), read on the host.
+ * No conjugation.  Built, like the reference's complex fragments, from four real
+ * error-corrected products (include/wmma_extension/tcec/complex.hpp:646-727:
+ * real = Ar Br + Ai (-Bi), imag = Ai Br + Ar Bi; its test is test/tcec/mma_complex.cu);
+ * here each part is one real GEMM over the concatenated K of its two products, so the
+ * promotion rule sees K' = 2K.  Scratch (operand panels and two m x n planes) comes from
+ * the per-stream workspace.
+ */
+int tcec_cgemm(int layout_a, int layout_b, int layout_c, int m, int n, int k, const float* alpha,
+               const float* a, long long lda, const float* b, long long ldb, const float* beta, float* c,
+               long long ldc, int policy, void* stream);
+
+/*
  * Element-wise split, exposed so the split can be checked bit for bit:
  *   hi[i] = cast<T>(in[i]);  lo[i] = cast<T>((in[i] - hi[i]) * s)
  * returned widened to float (lo still carries the scale s = 2^11 for fp16, 1 for

@@ -93,6 +93,21 @@ def tcec_gemm(a: np.ndarray, b: np.ndarray, c: np.ndarray | None = None, alpha: 
     return out
 
 
+def tcec_cgemm(a: np.ndarray, b: np.ndarray, policy: str = "fp16_ec", rn_block: int = 1) -> np.ndarray:
+    """Complex product from four real TCEC products in the reference's order
+    (include/wmma_extension/tcec/complex.hpp:712-727): imag = Ai Br, then += Ar Bi;
+    real = Ar Br, then += Ai (-Bi).  Returns a complex64 (m, n) array."""
+    a = np.asarray(a, dtype=np.complex64)
+    b = np.asarray(b, dtype=np.complex64)
+    ar, ai = np.ascontiguousarray(a.real), np.ascontiguousarray(a.imag)
+    br, bi = np.ascontiguousarray(b.real), np.ascontiguousarray(b.imag)
+    im = tcec_gemm(ai, br, policy=policy, rn_block=rn_block)
+    im = tcec_gemm(ar, bi, c=im, beta=1.0, policy=policy, rn_block=rn_block)
+    re = tcec_gemm(ar, br, policy=policy, rn_block=rn_block)
+    re = tcec_gemm(ai, -bi, c=re, beta=1.0, policy=policy, rn_block=rn_block)
+    return (re + 1j * im).astype(np.complex64)
+
+
 def gemm_f64(a: np.ndarray, b: np.ndarray, row0: int = 0, row1: int | None = None) -> np.ndarray:
     """FP64 ground truth for rows [row0, row1) of A @ B."""
     a = np.asarray(a, dtype=np.float32)

@@ -252,6 +252,92 @@ def test_cta_pair_kernel_is_bit_identical(shape, policy):
     assert torch.equal(got, want)
 
 
+# ---------------------------------------------------------------- complex GEMM
+def _crand(rng, shape):
+    return (rng.uniform(-1, 1, shape) + 1j * rng.uniform(-1, 1, shape)).astype(np.complex64)
+
+
+@pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec", "fp16_no_ec"])
+@pytest.mark.parametrize("shape", [(32, 32, 32), (130, 257, 33), (256, 512, 300), (1, 1, 1), (500, 300, 1000)])
+def test_cgemm_matches_oracle_and_complex128(policy, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(500 + m + n + k)
+    a, b = _crand(rng, (m, k)), _crand(rng, (k, n))
+    exact = a.astype(np.complex128) @ b.astype(np.complex128)
+    got = tcec.cgemm(_t(a), _t(b), policy=policy)
+    tcec.device_status()
+    got = got.cpu().numpy()
+    scale = np.max(np.abs(exact))
+    e_got = np.max(np.abs(got - exact)) / scale
+    want = cpu.tcec_cgemm(a, b, policy=policy)
+    e_orc = np.max(np.abs(want - exact)) / scale
+    if policy.endswith("no_ec"):
+        assert e_got < 2e-3 and e_got < 2 * e_orc + 1e-6
+    else:
+        assert e_got < 1e-6
+        assert np.max(np.abs(got - want)) <= 2e-6 * max(1.0, scale)
+        # the FP32 class: torch's complex64 product of the same operands
+        e_f32 = np.max(np.abs((_t(a) @ _t(b)).cpu().numpy() - exact)) / scale
+        assert e_got <= 2 * max(e_orc, e_f32)
+        if m == n == k == 32:
+            assert np.max(np.abs(got - exact)) < 1e-5 * np.sqrt(2)  # threshold of test/tcec/mma_complex.cu per part
+
+
+@pytest.mark.parametrize("la", ["row", "col"])
+@pytest.mark.parametrize("lb", ["row", "col"])
+@pytest.mark.parametrize("lc", ["row", "col"])
+def test_cgemm_layouts_alpha_beta(la, lb, lc):
+    m, n, k = 150, 200, 70
+    rng = np.random.default_rng(77)
+    a, b, c0 = _crand(rng, (m, k)), _crand(rng, (k, n)), _crand(rng, (m, n))
+    alpha, beta = 0.5 - 1.25j, -0.75 + 2j
+
+    def place(x, layout, pad):
+        r, c = x.shape
+        if layout == "row":
+            buf = torch.full((r, c + pad), 7 + 7j, dtype=torch.complex64, device=DEV)
+            view = buf[:, :c]
+        else:
+            buf = torch.full((c, r + pad), 7 + 7j, dtype=torch.complex64, device=DEV)
+            view = buf.t()[:r, :]
+        view.copy_(_t(x))
+        return buf, view
+
+    _, av = place(a, la, 3)
+    _, bv = place(b, lb, 5)
+    cbuf, cv = place(c0, lc, 2)
+    tcec.cgemm(av, bv, cv, alpha=alpha, beta=beta)
+    tcec.device_status()
+    exact = alpha * (a.astype(np.complex128) @ b.astype(np.complex128)) + beta * c0.astype(np.complex128)
+    got = cv.cpu().numpy()
+    assert np.max(np.abs(got - exact)) / np.max(np.abs(exact)) < 1e-6
+    # the padding of C is untouched
+    pad = cbuf[:, -2:].cpu().numpy()
+    assert np.all(pad == 7 + 7j)
+    # alpha = 0 scales only; k = 0 likewise
+    tcec.cgemm(av, bv, cv, alpha=0.0, beta=2.0)
+    tcec.device_status()
+    assert np.allclose(cv.cpu().numpy(), 2 * got, rtol=1e-6, atol=1e-6)
+
+
+def test_cgemm_full_size_linearity():
+    """4096^3 complex: sampled rows against complex128 and C(A, B1 + B2) = C(A, B1) + C(A, B2) to rounding."""
+    n = 4096
+    g = torch.Generator(device=DEV).manual_seed(11)
+    def crand():
+        return torch.complex(torch.rand(n, n, device=DEV, generator=g) * 2 - 1,
+                             torch.rand(n, n, device=DEV, generator=g) * 2 - 1)
+    a, b1, b2 = crand(), crand(), crand()
+    c1, c2, c12 = tcec.cgemm(a, b1), tcec.cgemm(a, b2), tcec.cgemm(a, b1 + b2)
+    tcec.device_status()
+    rows = torch.tensor([0, 1, 127, 128, 2049, 4095], device=DEV)
+    exact = a[rows].to(torch.complex128) @ b1.to(torch.complex128)
+    err = ((c1[rows].to(torch.complex128) - exact).abs().max() / exact.abs().max()).item()
+    assert err < 1e-6
+    lin = ((c12 - (c1 + c2)).abs().max() / c12.abs().max()).item()
+    assert lin < 2e-6
+
+
 # ---------------------------------------------------------------- golden fixtures of the reference
 def test_against_reference_warp_fixtures(golden_dir):
     g = np.load(os.path.join(golden_dir, "ref_warp_mma.npz"))

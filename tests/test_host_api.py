@@ -51,6 +51,11 @@ def test_invalid_arguments_are_rejected_without_a_device():
     assert lib.tcec_sgemm_batched(0, 0, 0, 4, 4, 4, 1.0, z, 4, z, 4, 0.0, z, 4, 0, 0, z) == tcec.OK
     assert lib.tcec_split(z, z, z, 0, 0, z) == tcec.OK
     assert lib.tcec_split(z, z, z, 5, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    one = (ctypes.c_float * 2)(1.0, 0.0)
+    assert lib.tcec_cgemm(0, 0, 0, 4, 4, 4, None, p, 4, p, 4, one, p, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_cgemm(0, 0, 0, 4, 4, 4, one, p, 3, p, 4, one, p, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_cgemm(0, 3, 0, 4, 4, 4, one, p, 4, p, 4, one, p, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
+    assert lib.tcec_cgemm(0, 0, 0, 0, 4, 4, one, z, 4, z, 4, one, z, 4, 0, z) == tcec.OK
     assert lib.tcec_pack_a(0, 4, 4, z, 4, z, 0, z) == tcec.ERR_INVALID_ARGUMENT
     assert lib.tcec_sgemm_packed(0, 4, 4, 4, 1.0, z, z, 0.0, z, 4, 0, z) == tcec.ERR_INVALID_ARGUMENT
 

@@ -120,6 +120,19 @@ def test_restatement_error_levels(policy, bound):
     assert cpu.errors(got, 0.5 * exact - 2.0 * c0)["max_rel"] < bound * 2
 
 
+@pytest.mark.parametrize("policy,bound", [("fp16_ec", 1e-6), ("tf32_ec", 1e-6), ("fp16_no_ec", 2e-3)])
+def test_complex_product_from_four_real_products(policy, bound):
+    """The reference's complex fragments (complex.hpp:646-727; threshold of test/tcec/mma_complex.cu)."""
+    rng = np.random.default_rng(21)
+    a = (rng.uniform(-1, 1, (32, 32)) + 1j * rng.uniform(-1, 1, (32, 32))).astype(np.complex64)
+    b = (rng.uniform(-1, 1, (32, 32)) + 1j * rng.uniform(-1, 1, (32, 32))).astype(np.complex64)
+    exact = a.astype(np.complex128) @ b.astype(np.complex128)
+    got = cpu.tcec_cgemm(a, b, policy=policy)
+    assert np.max(np.abs(got - exact)) / np.max(np.abs(exact)) < bound
+    if not policy.endswith("no_ec"):
+        assert np.max(np.abs(got - exact)) < 1e-5 * np.sqrt(2)
+
+
 def test_wide_exponent_inputs():
     """The 16384^3 configuration's value distribution, sign * U[1,2) * 2^U{-15..15}: tf32 keeps
     the FP32 exponent range; fp16 heads overflow to inf from 65520 up (reference semantics,

@@ -196,9 +196,17 @@ void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
 bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
 
 // Split one operand (A: rows = m; B: rows = n) into panels on `stream`.
+// `part` describes an operand that is one half of a K-concatenated panel set built from
+// interleaved complex data: element stride 2, a sign, and where its k blocks go.
+struct PackPart {
+  int elem_stride = 1;
+  float mul = 1.0f;
+  int kb_offset = 0;
+  int nkb_out = 0;
+};
 void pack_operand(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
                   long long ld, long long stride, int batch, uint8_t* panels, size_t panels_stride,
-                  int policy, cudaStream_t stream) {
+                  int policy, cudaStream_t stream, const PackPart& part = PackPart()) {
   const int kop = policy_tf32(policy) ? 16 : 32;
   SplitParams sp{};
   sp.src = src;
@@ -212,7 +220,10 @@ void pack_operand(bool k_contiguous, int rows, int k, const float* src, const fl
   sp.nkb = (k + kop - 1) / kop;
   sp.panels = panels;
   sp.panels_batch_stride = static_cast<long long>(panels_stride);
-  sp.mul = 1.0f;
+  sp.mul = part.mul;
+  sp.elem_stride = part.elem_stride;
+  sp.kb_offset = part.kb_offset;
+  sp.nkb_out = part.nkb_out;
   if (policy_tf32(policy)) {
     if (policy_ec(policy)) launch_split<true, true>(sp, batch, stream);
     else launch_split<true, false>(sp, batch, stream);
@@ -416,6 +427,102 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
   return TCEC_OK;
 }
 
+// ---------------------------------------------------------------- complex GEMM (four real products)
+// C = alpha * (Pr + i Pi) + beta * C on interleaved complex C; Pr, Pi are dense planar products.
+__global__ void cgemm_combine_kernel(const float* __restrict__ pr, const float* __restrict__ pi, float2* c,
+                                     long long ldc, int inner, int outer, float2 alpha, float2 beta,
+                                     int has_product) {
+  for (int o = blockIdx.y; o < outer; o += gridDim.y)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inner; i += gridDim.x * blockDim.x) {
+      float2* dst = c + static_cast<long long>(o) * ldc + i;
+      float2 out = make_float2(0.f, 0.f);
+      if (has_product) {
+        const long long q = static_cast<long long>(o) * inner + i;
+        const float xr = pr[q], xi = pi[q];
+        out.x = alpha.x * xr - alpha.y * xi;
+        out.y = alpha.x * xi + alpha.y * xr;
+      }
+      if (beta.x != 0.f || beta.y != 0.f) {
+        const float2 old = *dst;
+        out.x += beta.x * old.x - beta.y * old.y;
+        out.y += beta.x * old.y + beta.y * old.x;
+      }
+      *dst = out;
+    }
+}
+
+// The reference builds a complex product from four real TCEC products
+// (include/wmma_extension/tcec/complex.hpp:646-727): real = Ar Br + Ai (-Bi), imag = Ai Br + Ar Bi.
+// Here the two products of each part become ONE real GEMM over a K of twice the length:
+// [Ar | Ai] x [Br ; -Bi] and [Ar | Ai] x [Bi ; Br].  A is split once into a concatenated panel
+// set, B into two; both GEMMs run through the real kernel into planar scratch, and an
+// elementwise pass applies the complex alpha and beta into the interleaved C.
+int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, const float* a, long long lda,
+               const float* b, long long ldb, const float* beta, float* c, long long ldc, int policy,
+               void* stream_v) {
+  if (bad_layout(la) || bad_layout(lb) || bad_layout(lc) || m < 0 || n < 0 || k < 0 || policy < 0 ||
+      policy > 3 || !alpha || !beta)
+    return TCEC_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0) return TCEC_OK;
+  if (!c || ldc < (lc == TCEC_ROW_MAJOR ? n : m)) return TCEC_ERR_INVALID_ARGUMENT;
+  const bool has_product = k > 0 && (alpha[0] != 0.f || alpha[1] != 0.f);
+  if (has_product) {
+    if (!a || !b) return TCEC_ERR_INVALID_ARGUMENT;
+    if (lda < (la == TCEC_ROW_MAJOR ? k : m) || ldb < (lb == TCEC_ROW_MAJOR ? n : k))
+      return TCEC_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != TCEC_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int inner = lc == TCEC_ROW_MAJOR ? n : m, outer = lc == TCEC_ROW_MAJOR ? m : n;
+  const dim3 cgrid((inner + 255) / 256, outer < 32768 ? outer : 32768);
+  const float2 al = make_float2(alpha[0], alpha[1]), be = make_float2(beta[0], beta[1]);
+  if (!has_product) {
+    cgemm_combine_kernel<<<cgrid, 256, 0, stream>>>(nullptr, nullptr, reinterpret_cast<float2*>(c), ldc, inner,
+                                                    outer, al, be, 0);
+    TCEC_CUDA(cudaGetLastError());
+    return TCEC_OK;
+  }
+  const int kop = policy_tf32(policy) ? 16 : 32;
+  const int nkb = (k + kop - 1) / kop;
+  const long long k2_ll = 2ll * nkb * kop;
+  if (k2_ll > 0x7fffffff) return TCEC_ERR_INVALID_ARGUMENT;
+  const int k2 = static_cast<int>(k2_ll);
+  const Shape s = plan(m, n, k2, policy);
+  const size_t plane = ((static_cast<size_t>(m) * n * sizeof(float)) + 255) & ~static_cast<size_t>(255);
+  void* ws = nullptr;
+  rc = get_workspace(st, stream, s.a_bytes + 2 * s.b_bytes + 2 * plane, &ws);
+  if (rc != TCEC_OK) return rc;
+  uint8_t* pa = static_cast<uint8_t*>(ws);
+  uint8_t* pbr = pa + s.a_bytes;
+  uint8_t* pbi = pbr + s.b_bytes;
+  float* prod_r = reinterpret_cast<float*>(pbi + s.b_bytes);
+  float* prod_i = reinterpret_cast<float*>(pbi + s.b_bytes + plane);
+  const bool a_kc = (la == TCEC_ROW_MAJOR), b_kc = (lb == TCEC_COL_MAJOR);
+  PackPart first, second;
+  first.elem_stride = second.elem_stride = 2;
+  first.nkb_out = second.nkb_out = 2 * nkb;
+  second.kb_offset = nkb;
+  // A' = [Ar | Ai]
+  pack_operand(a_kc, m, k, a, nullptr, 2 * lda, 0, 1, pa, 0, policy, stream, first);
+  pack_operand(a_kc, m, k, a + 1, nullptr, 2 * lda, 0, 1, pa, 0, policy, stream, second);
+  // B'r = [Br ; -Bi], B'i = [Bi ; Br]
+  pack_operand(b_kc, n, k, b, nullptr, 2 * ldb, 0, 1, pbr, 0, policy, stream, first);
+  PackPart neg = second;
+  neg.mul = -1.0f;
+  pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbr, 0, policy, stream, neg);
+  pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, first);
+  pack_operand(b_kc, n, k, b, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, second);
+  gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbr, 0, 0.0f, prod_r, nullptr, inner, 0, lc, 1, policy, st, stream);
+  gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbi, 0, 0.0f, prod_i, nullptr, inner, 0, lc, 1, policy, st, stream);
+  cgemm_combine_kernel<<<cgrid, 256, 0, stream>>>(prod_r, prod_i, reinterpret_cast<float2*>(c), ldc, inner,
+                                                  outer, al, be, 1);
+  TCEC_CUDA(cudaGetLastError());
+  return TCEC_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -531,6 +638,12 @@ int tcec_sgemm_batched_cublas(int transa, int transb, int m, int n, int k, const
     return TCEC_ERR_INVALID_ARGUMENT;
   return gemm_impl(la, lb, TCEC_COL_MAJOR, m, n, k, *alpha, nullptr, a_array, lda, 0, nullptr, b_array, ldb, 0,
                    *beta, nullptr, c_array, ldc, 0, batch, policy, stream);
+}
+
+int tcec_cgemm(int layout_a, int layout_b, int layout_c, int m, int n, int k, const float* alpha, const float* a,
+               long long lda, const float* b, long long ldb, const float* beta, float* c, long long ldc,
+               int policy, void* stream) {
+  return cgemm_impl(layout_a, layout_b, layout_c, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, policy, stream);
 }
 
 int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, void* stream) {

@@ -72,6 +72,10 @@ struct SplitParams {
   uint8_t* panels;               // output
   long long panels_batch_stride; // bytes
   float mul;                     // value multiplied in before the split (1 for plain loads)
+  int elem_stride;               // floats between consecutive elements (0 or 1: dense; 2: one part of
+                                 // interleaved complex data, `src` pointing at that part)
+  int kb_offset;                 // first k block written (operands concatenated along K)
+  int nkb_out;                   // k blocks per row block in the destination (0: nkb)
 };
 
 // grid = (nkb, row_blocks, batch), 256 threads: one CTA writes one hi(+lo) panel.
@@ -83,9 +87,11 @@ __global__ void __launch_bounds__(256) tcec_split_panels_kernel(const SplitParam
   const float* __restrict__ src =
       p.src_array ? p.src_array[b] : p.src + static_cast<long long>(b) * p.batch_stride;
   uint8_t* out = p.panels + static_cast<long long>(b) * p.panels_batch_stride +
-                 (static_cast<size_t>(rb) * p.nkb + kb) * (kEc ? 2 : 1) * kPanelBytes;
+                 (static_cast<size_t>(rb) * (p.nkb_out ? p.nkb_out : p.nkb) + p.kb_offset + kb) *
+                     (kEc ? 2 : 1) * kPanelBytes;
   const int k0 = kb * KOP;
-  const bool vec_ok = (p.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  const int es = p.elem_stride > 1 ? p.elem_stride : 1;
+  const bool vec_ok = (es == 1) && (p.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
     const int item = threadIdx.x + it * 256;  // 512 (row, chunk) items per panel
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(256) tcec_split_panels_kernel(const SplitParam
     const int kk = k0 + c * KCH;
     float v[KCH];
     if (p.k_contiguous) {
-      const float* s = src + static_cast<long long>(row) * p.ld + kk;
+      const float* s = src + static_cast<long long>(row) * p.ld + static_cast<long long>(kk) * es;
       if (row < p.rows && kk + KCH <= p.k && vec_ok) {
 #pragma unroll
         for (int q = 0; q < KCH / 4; ++q) {
@@ -113,13 +119,13 @@ __global__ void __launch_bounds__(256) tcec_split_panels_kernel(const SplitParam
         }
       } else {
 #pragma unroll
-        for (int q = 0; q < KCH; ++q) v[q] = (row < p.rows && kk + q < p.k) ? __ldg(s + q) : 0.f;
+        for (int q = 0; q < KCH; ++q) v[q] = (row < p.rows && kk + q < p.k) ? __ldg(s + q * es) : 0.f;
       }
     } else {
 #pragma unroll
       for (int q = 0; q < KCH; ++q)
         v[q] = (row < p.rows && kk + q < p.k)
-                   ? __ldg(src + static_cast<long long>(kk + q) * p.ld + row)
+                   ? __ldg(src + static_cast<long long>(kk + q) * p.ld + static_cast<long long>(row) * es)
                    : 0.f;
     }
     if (p.mul != 1.0f) {

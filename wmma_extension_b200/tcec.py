@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "tcec_pack_b",
     "tcec_sgemm_packed",
     "tcec_split",
+    "tcec_cgemm",
     "tcec_sgemm_cublas",
     "tcec_sgemm_batched_cublas",
     "tcec_sgemm_static",
@@ -95,6 +96,8 @@ def load() -> ctypes.CDLL:
     lib.tcec_static_scratch_bytes.restype = sz
     lib.tcec_static_status.argtypes = [ctypes.POINTER(i)]
     lib.tcec_static_status.restype = i
+    lib.tcec_cgemm.argtypes = [i, i, i, i, i, i, fp, p, ll, p, ll, fp, p, ll, i, p]
+    lib.tcec_cgemm.restype = i
     lib.tcec_split.argtypes = [p, p, p, sz, i, p]
     lib.tcec_split.restype = i
     lib.tcec_set_option.argtypes = [ctypes.c_char_p, i]
@@ -188,6 +191,30 @@ def sgemm(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *,
         st = load().tcec_sgemm(la, lb, lc, m, n, k, alpha, a.data_ptr(), lda, b.data_ptr(), ldb, beta,
                                c.data_ptr(), ldc, _policy(policy), _stream_ptr())
     _check(st, "tcec_sgemm")
+    return c
+
+
+def cgemm(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, *, alpha: complex = 1.0,
+          beta: complex = 0.0, policy="fp16_ec") -> torch.Tensor:
+    """C = alpha * A @ B + beta * C for 2-D complex64 CUDA tensors (row- or column-major views)."""
+    for t in (a, b) + ((c,) if c is not None else ()):
+        if not t.is_cuda or t.dtype != torch.complex64:
+            raise ValueError("operands must be complex64 CUDA tensors")
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2:
+        raise ValueError("inner dimensions differ")
+    if c is None:
+        c = torch.empty((m, n), dtype=torch.complex64, device=a.device)
+    la, lda = _layout_ld(a)
+    lb, ldb = _layout_ld(b)
+    lc, ldc = _layout_ld(c)
+    al = (ctypes.c_float * 2)(complex(alpha).real, complex(alpha).imag)
+    be = (ctypes.c_float * 2)(complex(beta).real, complex(beta).imag)
+    with torch.cuda.device(a.device):
+        st = load().tcec_cgemm(la, lb, lc, m, n, k, al, a.data_ptr(), lda, b.data_ptr(), ldb, be,
+                               c.data_ptr(), ldc, _policy(policy), _stream_ptr())
+    _check(st, "tcec_cgemm")
     return c
 
 
