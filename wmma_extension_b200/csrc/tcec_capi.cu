@@ -361,12 +361,13 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   fp.c_batch_stride = stride_c;
   fp.c_col_major = (lc == TCEC_COL_MAJOR);
   fp.status = st->status;
+  fp.debug_flags = g_debug_flags;
   const long long ntiles = static_cast<long long>(fp.tiles_m) * fp.tiles_n * batch;
   const int grid = static_cast<int>(ntiles < st->sm_count ? ntiles : st->sm_count);
   if (policy_ec(policy))
-    tcec_gemm_fused_kernel<true><<<grid, 384, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+    tcec_gemm_fused_kernel<true><<<grid, GemmFusedCfg<true>::THREADS, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
   else
-    tcec_gemm_fused_kernel<false><<<grid, 384, GemmFusedCfg<false>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+    tcec_gemm_fused_kernel<false><<<grid, GemmFusedCfg<false>::THREADS, GemmFusedCfg<false>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
   return true;
 }
 

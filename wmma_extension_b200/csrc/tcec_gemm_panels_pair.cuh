@@ -32,7 +32,8 @@ struct GemmPairCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int NST_RAW = (200 * 1024) / STAGE_BYTES;
   static constexpr int NST = NST_RAW > 8 ? 8 : NST_RAW;
-  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + 1024;
+  static constexpr int EPI_OFFSET = NST * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + 8 * kEpiBufBytes + 1024;
   static constexpr int TMEM_COLS = kEc ? 512 : 256;
   static constexpr int THREADS = 384;
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
@@ -55,6 +56,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   __shared__ uint32_t abort_flag;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = (rank == 0);
@@ -310,7 +312,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
         tc_fence_after();
       }
       float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
-      const int row = tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32 + lane;
       const int col0 = tc.nt * BN + colbase;
       const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
       if constexpr (kEc) {
@@ -327,53 +328,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(corr_free_leader);
       }
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        if (row < p.M) {
-          if (!p.c_col_major) {
-            float* crow = cbase + static_cast<long long>(row) * p.ldc;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const int col = col0 + cc * 32 + i;
-              if (vec_ok && col + 3 < p.N) {
-                float4 o;
-                o.x = p.alpha * acc[cc * 32 + i + 0];
-                o.y = p.alpha * acc[cc * 32 + i + 1];
-                o.z = p.alpha * acc[cc * 32 + i + 2];
-                o.w = p.alpha * acc[cc * 32 + i + 3];
-                if (p.beta != 0.f) {
-                  const float4 old = *reinterpret_cast<const float4*>(crow + col);
-                  o.x += p.beta * old.x;
-                  o.y += p.beta * old.y;
-                  o.z += p.beta * old.z;
-                  o.w += p.beta * old.w;
-                }
-                *reinterpret_cast<float4*>(crow + col) = o;
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  if (col + e < p.N) {
-                    float o = p.alpha * acc[cc * 32 + i + e];
-                    if (p.beta != 0.f) o += p.beta * crow[col + e];
-                    crow[col + e] = o;
-                  }
-                }
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int col = col0 + cc * 32 + i;
-              if (col < p.N) {
-                float* dst = cbase + static_cast<long long>(col) * p.ldc + row;
-                float o = p.alpha * acc[cc * 32 + i];
-                if (p.beta != 0.f) o += p.beta * *dst;
-                *dst = o;
-              }
-            }
-          }
-        }
-      }
+      StoreTarget st;
+      st.cbase = cbase;
+      st.ldc = p.ldc;
+      st.M = p.M;
+      st.N = p.N;
+      st.col_major = p.c_col_major;
+      st.vec_ok = vec_ok;
+      st.alpha = p.alpha;
+      st.beta = p.beta;
+      store_warp_block(acc, tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32, col0, st, reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
     }
     if (!ok) {
       abort_flag = 1;
