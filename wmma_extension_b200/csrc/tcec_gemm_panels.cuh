@@ -66,6 +66,13 @@ struct GemmPanelCfg {
   static constexpr int SMEM_BYTES = NST * STAGE_BYTES + EPI_WARPS * kEpiBufBytes + 1024;
   static constexpr int TMEM_COLS = kEc ? 2 * BN : BN;  // 128, 256 or 512: powers of two
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
+  // 256-wide tiles run 384 threads (168 registers each at launch).  The control warpgroup needs
+  // few, so it hands registers to the two epilogue warpgroups (setmaxnreg; the shares sum to the
+  // launch allocation): with 232 the epilogue keeps two 32-column TMEM loads in flight next to
+  // its 128 running sums, which shortens every promotion.
+  static constexpr bool REBALANCE = (EPI_WARPS == 8);
+  static constexpr int REGS_CONTROL = 40, REGS_EPILOGUE = 232;
+  static_assert(!REBALANCE || 128 * REGS_CONTROL + 256 * REGS_EPILOGUE <= THREADS * 168, "register shares");
   static constexpr int GROUP_M = 16;                   // m tiles per raster group
 };
 
@@ -132,6 +139,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   volatile uint32_t* abortp = &abort_flag;
 
   if (warp < 4) {
+    if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_CONTROL>();
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -288,6 +296,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   }
   } else {
     // ------------------------------------------------------------ epilogue
+    if constexpr (Cfg::REBALANCE) setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     const int ew = warp - 4;
     const int q = warp & 3;          // TMEM lane quarter this warp may read
     const int colbase = (ew >> 2) * 128;
@@ -307,17 +316,40 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         }
         if (warp == 4 && lane == 0) trace_mark(p, 2, chunk);
         tc_fence_after();
+        if constexpr (Cfg::REBALANCE) {
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-          if (c == 0) {
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + (2 * h) * 32, v0);
+            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + (2 * h + 1) * 32, v1);
+            tmem_ld_wait();
+            if (c == 0) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
-          } else {
+              for (int i = 0; i < 32; ++i) {
+                acc[(2 * h) * 32 + i] = __uint_as_float(v0[i]);
+                acc[(2 * h + 1) * 32 + i] = __uint_as_float(v1[i]);
+              }
+            } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
+              for (int i = 0; i < 32; ++i) {
+                acc[(2 * h) * 32 + i] += __uint_as_float(v0[i]);
+                acc[(2 * h + 1) * 32 + i] += __uint_as_float(v1[i]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
+            tmem_ld_wait();
+            if (c == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
+            }
           }
         }
         tc_fence_before();
