@@ -48,68 +48,101 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs: NVML from a
+    thread every 10 ms (read-only queries), or nvidia-smi every 100 ms where NVML is missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.nvml = None
+        self.samples = []  # (sm_mhz, sm_max_mhz, power_w, set(reasons))
+        self.first = 0
+        self.last = None
+        self._stop = False
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
             self.thread.start()
-            t0 = time.time()
-            while not self.lines and time.time() - t0 < 5.0:
-                time.sleep(0.05)
-        except OSError:
-            self.proc = None
-        self.first = 0
-        self.last = None
+        except Exception:
+            self.nvml = None
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "100"],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._read_smi, daemon=True)
+                self.thread.start()
+            except OSError:
+                self.proc = None
+        t0 = time.time()
+        while not self.samples and time.time() - t0 < 5.0:
+            time.sleep(0.02)
 
-    def mark_begin(self):
-        self.first = len(self.lines)
+    def _poll_nvml(self):
+        n = self.nvml
+        masks = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        while not self._stop:
+            try:
+                clk = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                try:
+                    bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((float(clk), float(self.smax), pw, {k for k, m in masks.items() if bits & m}))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
-    def mark_end(self):
-        self.last = len(self.lines)
-
-    def _read(self):
+    def _read_smi(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        window = self.lines[self.first:self.last] if self.last and self.last > self.first else self.lines
-        for line in window:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-                power.append(float(parts[2]))
+                rec = (float(parts[0]), float(parts[1]), float(parts[2]),
+                       {nm for nm, val in zip(self.NAMES, parts[3:7]) if val.lower().startswith("active")})
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+            self.samples.append(rec)
+
+    def mark_begin(self):
+        self.first = len(self.samples)
+
+    def mark_end(self):
+        self.last = len(self.samples)
+
+    def stop(self):
+        self._stop = True
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.nvml is None and self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        window = self.samples[self.first:self.last] if self.last and self.last > self.first else self.samples
+        sm = [w[0] for w in window]
+        reasons = set()
+        for w in window:
+            reasons |= w[3]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(w[1] for w in window) if window else None,
+                "power_w_max": max(w[2] for w in window) if window else None,
+                "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvml 10 ms" if self.nvml is not None else "nvidia-smi 100 ms"}
 
 
 def make_uniform(torch, device, rows, cols, seed):
