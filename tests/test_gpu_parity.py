@@ -506,3 +506,90 @@ def test_full_size_sampled_rows_and_linearity():
         c2 = tcec.sgemm(a, b, alpha=2.0, policy=policy)
         assert torch.equal(c2, 2 * c)  # scaling by a power of two is exact
         del c, c2
+
+
+def _free_gib():
+    free, _ = torch.cuda.mem_get_info()
+    return free / 2 ** 30
+
+
+def test_batched_configuration_full_size_properties():
+    """8192 independent 256^3 products, N(0,1): first/last/sampled matrices against FP64, and the
+    row checksums of every matrix, C 1 = A (B 1), which no wrong tile anywhere can satisfy."""
+    if _free_gib() < 12:
+        pytest.skip("needs 12 GiB of free device memory")
+    nb, n = 8192, 256
+    g = torch.Generator(device=DEV).manual_seed(4)
+    a = torch.randn((nb, n, n), generator=g, device=DEV)
+    b = torch.randn((nb, n, n), generator=g, device=DEV)
+    c = tcec.sgemm_strided_batched(a, b)
+    tcec.device_status()
+    idx = [0, 1, 1023, 1024, 4095, 4096, 8190, 8191]
+    exact = torch.matmul(a[idx].double(), b[idx].double())
+    err = ((c[idx].double() - exact).abs().amax(dim=(1, 2)) / exact.abs().amax(dim=(1, 2))).max().item()
+    f32 = torch.matmul(a[idx], b[idx])
+    err32 = ((f32.double() - exact).abs().amax(dim=(1, 2)) / exact.abs().amax(dim=(1, 2))).max().item()
+    assert err < 1e-6 and err <= 2 * err32, (err, err32)
+    ones = torch.ones((nb, n, 1), dtype=torch.float64, device=DEV)
+    want = torch.matmul(a.double(), torch.matmul(b.double(), ones)).squeeze(-1)
+    got = c.double().sum(dim=2)
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() < 1e-4 * scale  # 256 terms of ~1e-7 relative error each
+    # the pointer-array form gives the same bits
+    c2 = [torch.empty((n, n), device=DEV) for _ in range(64)]
+    tcec.sgemm_batched(list(a[:64]), list(b[:64]), c2)
+    tcec.device_status()
+    # (the pointer-array form goes through the panel kernel: same products, same rounding points)
+    assert all(torch.allclose(x, y, rtol=0, atol=2e-5) for x, y in zip(c2, c[:64]))
+
+
+def test_column_block_configuration_full_size_properties():
+    """M = N = 65536, K = 8192, N(0,1) on one GPU in column blocks (what each rank of the sharded
+    configuration computes): sampled rows against FP64 and the row checksums of the whole result."""
+    if _free_gib() < 40:
+        pytest.skip("needs 40 GiB of free device memory")
+    m = n = 65536
+    k = 8192
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn((m, k), generator=g, device=DEV)
+    b = torch.randn((k, n), generator=g, device=DEV)
+    c = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    block = n // 8
+    for j in range(8):  # the eight column blocks of the 8-GPU sharding, through strided views of B and C
+        tcec.sgemm(a, b[:, j * block:(j + 1) * block], c[:, j * block:(j + 1) * block])
+    tcec.device_status()
+    rows = torch.tensor([0, 127, 128, 32767, 32768, 65535], device=DEV)
+    bd = b.double()
+    exact = a[rows].double() @ bd
+    err = ((c[rows].double() - exact).abs().max() / exact.abs().max()).item()
+    err32 = (((a[rows] @ b).double() - exact).abs().max() / exact.abs().max()).item()
+    assert err < 2e-6 and err <= 2 * err32, (err, err32)
+    want = a.double() @ (bd @ torch.ones((n, 1), dtype=torch.float64, device=DEV))
+    del bd
+    got = torch.zeros((m, 1), dtype=torch.float64, device=DEV)
+    for j in range(8):
+        got += c[:, j * block:(j + 1) * block].double().sum(dim=1, keepdim=True)
+    assert ((got - want).abs().max() / want.abs().max()).item() < 1e-5
+
+
+def test_column_sharded_driver_on_one_gpu(tmp_path):
+    """The multi-GPU driver with a world of one rank: row panels of A against a B packed once."""
+    import torch.distributed as dist
+    from wmma_extension_b200 import sharded
+
+    dist.init_process_group("gloo", init_method=f"file://{tmp_path}/store", rank=0, world_size=1)
+    try:
+        m, n, k = 700, 520, 300
+        g = torch.Generator(device=DEV).manual_seed(9)
+        a = torch.randn((m, k), generator=g, device=DEV)
+        b = torch.randn((k, n), generator=g, device=DEV)
+        c = torch.full((m, n), float("nan"), device=DEV)
+        sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=256)
+        tcec.device_status()
+        assert torch.equal(c, tcec.sgemm(a, b))
+        first, count = sharded.batch_shard(10, 0, 1)
+        ab, bb = torch.randn((10, 64, 96), device=DEV), torch.randn((10, 96, 130), device=DEV)
+        assert torch.equal(sharded.sgemm_batch_sharded(ab[first:first + count], bb[first:first + count]),
+                           tcec.sgemm_strided_batched(ab, bb))
+    finally:
+        dist.destroy_process_group()
