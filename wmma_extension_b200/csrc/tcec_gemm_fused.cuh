@@ -41,6 +41,7 @@
 #include "sm100_ptx.cuh"
 #include "tcec_epilogue.cuh"
 #include "tcec_gemm_panels.cuh"
+#include "tcec_gemm_roles.cuh"
 #include "tcec_panels.cuh"
 
 namespace tcec_sm100 {
@@ -228,51 +229,26 @@ __global__ void __launch_bounds__(640, 1)
     }
   } else if (warp < 4) {
     setmaxnreg_dec<Cfg::REGS_CONTROL>();
-    if (warp == 1 && lane == 0) {
-      // ---------------------------------------------------------- MMA issuer, main products
-      const uint32_t idesc = umma_idesc(0u, 128, BN);
-      const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-      uint32_t s = 0, ph = 0, chunk = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        int left_in_chunk = 0;
-        for (int kb = 0; kb < p.nkb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
-            ok = false;
-            break;
-          }
-          const bool first_in_chunk = (left_in_chunk == 0);
-          if (first_in_chunk) {
-            const int rest = p.nkb - kb;
-            left_in_chunk = (p.promo && p.promo < rest) ? p.promo : rest;
-            if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp, 0)) {
-              ok = false;
-              break;
-            }
-          }
-          tc_fence_after();
-          const uint32_t a16 = base16 + s * (Cfg::STAGE >> 4);
-          if (!(p.debug_flags & 2))
-#pragma unroll
-          for (uint32_t j = 0; j < 2; ++j)
-            umma_ss<false>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
-                           (first_in_chunk && j == 0) ? 0u : 1u);
-          if (--left_in_chunk == 0) {
-            umma_commit(smem_u32(&bar_main_full));
-            ++chunk;
-          }
-          umma_commit(smem_u32(&bar_empty[s]));
-          if (++s == static_cast<uint32_t>(NST)) {
-            s = 0;
-            ph ^= 1;
-          }
-        }
-      }
-      if (!ok) {
-        abort_flag = 1;
-        atomicCAS(p.status, 0, kErrMmaWait);
-        umma_commit(smem_u32(&bar_drain[0]));
-        mbar_wait_plain(smem_u32(&bar_drain[0]), 0);
+    if ((warp == 1 || (kEc && warp == 2)) && lane == 0) {
+      // ---------------------------------------------------------- MMA issuers (tcec_gemm_roles.cuh)
+      OperandImage im;
+      im.dconst = dconst;
+      im.base16 = (smem_base & 0x3ffff) >> 4;
+      im.stage16 = Cfg::STAGE >> 4;
+      im.a_lo16 = kALo;
+      im.b_hi16 = kBHi;
+      im.b_lo16 = kBLo;
+      im.idesc = umma_idesc(0u, 128, BN);
+      const TileWalk walk{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), ntiles, p.nkb, p.promo};
+      const RingBarriers ring{bar_full, bar_empty};
+      if (warp == 1) {
+        if (!issue_main_products<false, false, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+                                                    abortp, p.debug_flags, nullptr))
+          mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
+      } else {
+        if (!issue_corr_products<false, false, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+                                                    abortp, p.debug_flags, nullptr))
+          mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
       }
     } else if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer
@@ -315,52 +291,6 @@ __global__ void __launch_bounds__(640, 1)
         for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
           if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_landed[q]), (armed_parity >> q) & 1);
       }
-    } else if (warp == 2 && lane == 0) {
-      // ---------------------------------------------------------- MMA issuer, correction products
-      if constexpr (kEc) {
-        const uint32_t idesc = umma_idesc(0u, 128, BN);
-        const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-        uint32_t s = 0, ph = 0, tcount = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-          for (int kb = 0; kb < p.nkb; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
-              ok = false;
-              break;
-            }
-            if (kb == 0) {
-              if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
-                ok = false;
-                break;
-              }
-            }
-            tc_fence_after();
-            const uint32_t c16 = base16 + s * (Cfg::STAGE >> 4);
-            if (!(p.debug_flags & 2)) {
-#pragma unroll
-            for (uint32_t j = 0; j < 2; ++j)
-              umma_ss<false>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
-                             (kb == 0 && j == 0) ? 0u : 1u);
-#pragma unroll
-            for (uint32_t j = 0; j < 2; ++j)
-              umma_ss<false>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
-            }
-            umma_commit(smem_u32(&bar_empty[s]));
-            if (++s == static_cast<uint32_t>(NST)) {
-              s = 0;
-              ph ^= 1;
-            }
-          }
-          if (!ok) break;
-          umma_commit(smem_u32(&bar_corr_full));
-        }
-        if (!ok) {
-          abort_flag = 1;
-          atomicCAS(p.status, 0, kErrMmaWait);
-          umma_commit(smem_u32(&bar_drain[1]));
-          mbar_wait_plain(smem_u32(&bar_drain[1]), 0);
-        }
-      }
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -381,19 +311,7 @@ __global__ void __launch_bounds__(640, 1)
           break;
         }
         tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-          if (c == 0) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
-          }
-        }
+        promote_main_chunk<false>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_main_free));
@@ -405,15 +323,7 @@ __global__ void __launch_bounds__(640, 1)
           break;
         }
         tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * (1.0f / 2048.0f);
-        }
+        fold_correction(acc, tmem_corr + lane_addr + colbase, 1.0f / 2048.0f);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));

@@ -26,6 +26,7 @@
 #pragma once
 #include "sm100_ptx.cuh"
 #include "tcec_epilogue.cuh"
+#include "tcec_gemm_roles.cuh"
 #include "tcec_panels.cuh"
 
 namespace tcec_sm100 {
@@ -185,112 +186,28 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
           if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_full[q]), (armed_parity >> q) & 1);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer, main products
-    // Kept to a handful of integer instructions per MMA: descriptors are a constant OR-ed
-    // with a 14-bit address field, ring positions and the promotion interval are counters.
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
-      const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
-      constexpr uint32_t kBHi = Cfg::A_BYTES >> 4;
-      const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-      uint32_t it = 0, s = 0, ph = 0, chunk = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        int left_in_chunk = 0;  // k blocks still to issue in the current chunk
-        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32u)) {
-            ok = false;
-            break;
-          }
-          trace_mark(p, 0, it);
-          const bool first_in_chunk = (left_in_chunk == 0);
-          if (first_in_chunk) {
-            const int rest = p.nkb - kb;
-            left_in_chunk = (p.promo && p.promo < rest) ? p.promo : rest;
-            if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp, 0)) {
-              ok = false;
-              break;
-            }
-            trace_mark(p, 1, chunk);
-          }
-          tc_fence_after();
-          const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
-          if (!(p.debug_flags & 2))
-#pragma unroll
-          for (uint32_t j = 0; j < 2; ++j)
-            umma_ss<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
-                           (first_in_chunk && j == 0) ? 0u : 1u);
-          if (--left_in_chunk == 0) {
-            umma_commit(smem_u32(&bar_main_full));
-            ++chunk;
-          }
-          umma_commit(smem_u32(&bar_empty[s]));
-          trace_mark(p, 5, it);
-          if (++s == static_cast<uint32_t>(NST)) {
-            s = 0;
-            ph ^= 1;
-          }
-        }
-      }
-      if (!ok) {
-        abort_flag = 1;
-        atomicCAS(p.status, 0, kErrMmaWait);
-        // Nothing may still be writing TMEM when it is released below.
-        umma_commit(smem_u32(&bar_drain[0]));
-        mbar_wait_plain(smem_u32(&bar_drain[0]), 0);
-      }
-    }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------ MMA issuer, correction products
-    if constexpr (kEc) {
-      if (lane == 0) {
-        const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
-        const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
-        constexpr uint32_t kALo = kPanelBytes >> 4, kBHi = Cfg::A_BYTES >> 4,
-                           kBLo = (Cfg::A_BYTES + Cfg::NB * kPanelBytes) >> 4;
-        const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-        uint32_t s = 0, ph = 0, tcount = 0, cit = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-          for (int kb = 0; kb < p.nkb; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32u)) {
-              ok = false;
-              break;
-            }
-            if (kb == 0) {
-              if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
-                ok = false;
-                break;
-              }
-            }
-            trace_mark(p, 4, cit++);
-            tc_fence_after();
-            const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
-            if (!(p.debug_flags & 2)) {
-#pragma unroll
-            for (uint32_t j = 0; j < 2; ++j)
-              umma_ss<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
-                             (kb == 0 && j == 0) ? 0u : 1u);
-#pragma unroll
-            for (uint32_t j = 0; j < 2; ++j)
-              umma_ss<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
-            }
-            umma_commit(smem_u32(&bar_empty[s]));
-            if (++s == static_cast<uint32_t>(NST)) {
-              s = 0;
-              ph ^= 1;
-            }
-          }
-          if (!ok) break;
-          umma_commit(smem_u32(&bar_corr_full));
-        }
-        if (!ok) {
-          abort_flag = 1;
-          atomicCAS(p.status, 0, kErrMmaWait);
-          umma_commit(smem_u32(&bar_drain[1]));
-          mbar_wait_plain(smem_u32(&bar_drain[1]), 0);
-        }
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------ MMA issuers (tcec_gemm_roles.cuh)
+    if (lane == 0 && (warp == 1 || kEc)) {
+      OperandImage im;
+      im.dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+      im.base16 = (smem_base & 0x3ffff) >> 4;
+      im.stage16 = Cfg::STAGE_BYTES >> 4;
+      im.a_lo16 = kPanelBytes >> 4;
+      im.b_hi16 = Cfg::A_BYTES >> 4;
+      im.b_lo16 = (Cfg::A_BYTES + Cfg::NB * kPanelBytes) >> 4;
+      im.idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
+      const TileWalk walk{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), ntiles, p.nkb, p.promo};
+      const RingBarriers ring{bar_full, bar_empty};
+      unsigned long long* trace = blockIdx.x == 0 ? p.trace : nullptr;
+      if (warp == 1) {
+        if (!issue_main_products<kTf32, false, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+                                                    abortp, p.debug_flags, trace))
+          mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
+      } else {
+        if (!issue_corr_products<kTf32, false, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+                                                    abortp, p.debug_flags, trace))
+          mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
       }
     }
   }
@@ -316,42 +233,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         }
         if (warp == 4 && lane == 0) trace_mark(p, 2, chunk);
         tc_fence_after();
-        if constexpr (Cfg::REBALANCE) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t v0[32], v1[32];
-            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + (2 * h) * 32, v0);
-            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + (2 * h + 1) * 32, v1);
-            tmem_ld_wait();
-            if (c == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                acc[(2 * h) * 32 + i] = __uint_as_float(v0[i]);
-                acc[(2 * h + 1) * 32 + i] = __uint_as_float(v1[i]);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                acc[(2 * h) * 32 + i] += __uint_as_float(v0[i]);
-                acc[(2 * h + 1) * 32 + i] += __uint_as_float(v1[i]);
-              }
-            }
-          }
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
-            tmem_ld_wait();
-            if (c == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
-            }
-          }
-        }
+        promote_main_chunk<Cfg::REBALANCE>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_main_free));
@@ -371,15 +253,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       if constexpr (kEc) {
         // Fold the correction term into the registers first and hand the accumulator back
         // before the stores: the next tile's correction MMAs then overlap this tile's stores.
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * corr_scale;
-        }
+        fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));

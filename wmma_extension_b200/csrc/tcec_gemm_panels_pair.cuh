@@ -21,6 +21,7 @@
 #pragma once
 #include "sm100_ptx.cuh"
 #include "tcec_gemm_panels.cuh"
+#include "tcec_gemm_roles.cuh"
 
 namespace tcec_sm100 {
 
@@ -38,10 +39,6 @@ struct GemmPairCfg {
   static constexpr int THREADS = 384;
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
 };
-
-__device__ __forceinline__ void pair_trace(const GemmPanelParams& p, int role, uint32_t idx) {
-  if (p.trace && (blockIdx.x >> 1) == 0 && idx < 4096) p.trace[role * 4096 + idx] = clock64();
-}
 
 // p.tiles_m counts 256-row pair tiles here.
 template <bool kTf32, bool kEc>
@@ -88,6 +85,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   const uint32_t tmem_main = tmem_base_s;
   const uint32_t tmem_corr = tmem_base_s + BN;
   volatile uint32_t* abortp = &abort_flag;
+  // What the leader's two MMA threads need (tcec_gemm_roles.cuh): M = 256 across the pair.
+  OperandImage im;
+  im.dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
+  im.base16 = (smem_base & 0x3ffff) >> 4;
+  im.stage16 = Cfg::STAGE_BYTES >> 4;
+  im.a_lo16 = kPanelBytes >> 4;
+  im.b_hi16 = Cfg::A_BYTES >> 4;
+  im.b_lo16 = (Cfg::A_BYTES + kPanelBytes) >> 4;
+  im.idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
+  const TileWalk walk{pair, npairs, ntiles, p.nkb, p.promo};
+  const RingBarriers ring{bar_full, bar_empty};
 
   if (warp < 4) {
     if (warp == 0) {
@@ -106,7 +114,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
               ok = false;
               break;
             }
-            pair_trace(p, leader ? 2 : 3, it);
             if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {  // timing experiment: no loads
               mbar_arrive(smem_u32(&bar_full[s]));
               if (++s == static_cast<uint32_t>(NST)) {
@@ -147,7 +154,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
                 ok = false;
                 break;
               }
-              pair_trace(p, 1, it);
               mbar_arrive_cluster(map_to_cta(smem_u32(&bar_full[s]), 0));
               if (++s == static_cast<uint32_t>(NST)) {
                 s = 0;
@@ -161,106 +167,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           }
         } else {
           // -------------------------------------------------------- leader: main products
-          const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
-          const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
-          constexpr uint32_t kBHi = Cfg::A_BYTES >> 4;
-          const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-          uint32_t s = 0, ph = 0, chunk = 0, it = 0;
-          bool ok = true;
-          for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-            int left_in_chunk = 0;
-            for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-              if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
-                ok = false;
-                break;
-              }
-              pair_trace(p, 0, it);
-              const bool first_in_chunk = (left_in_chunk == 0);
-              if (first_in_chunk) {
-                const int rest = p.nkb - kb;
-                left_in_chunk = (p.promo && p.promo < rest) ? p.promo : rest;
-                if (!mbar_wait(smem_u32(&bar_main_free), (chunk & 1) ^ 1, abortp, 0)) {
-                  ok = false;
-                  break;
-                }
-              }
-              tc_fence_after();
-              const uint32_t a16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
-              if (!(p.debug_flags & 2))  // timing experiment: no MMAs
-#pragma unroll
-              for (uint32_t j = 0; j < 2; ++j)
-                umma_ss_pair<kTf32>(tmem_main, dconst | (a16 + 16 * j), dconst | (a16 + kBHi + 16 * j), idesc,
-                                    (first_in_chunk && j == 0) ? 0u : 1u);
-              if (--left_in_chunk == 0) {
-                umma_commit_pair(smem_u32(&bar_main_full));
-                ++chunk;
-              }
-              umma_commit_pair(smem_u32(&bar_empty[s]));
-              pair_trace(p, 5, it);
-              if (++s == static_cast<uint32_t>(NST)) {
-                s = 0;
-                ph ^= 1;
-              }
-            }
-          }
-          if (!ok) {
-            abort_flag = 1;
-            atomicCAS(p.status, 0, kErrMmaWait);
-            umma_commit_pair(smem_u32(&bar_drain[0]));
-            mbar_wait_plain(smem_u32(&bar_drain[0]), 0);
-          }
+          if (!issue_main_products<kTf32, true, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+                                                     abortp, p.debug_flags, nullptr))
+            mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
         }
       }
     } else if (warp == 2) {
       // ---------------------------------------------------------- leader: correction products
       if constexpr (kEc) {
         if (lane == 0 && leader) {
-          const uint32_t idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
-          const uint64_t dconst = umma_desc_kmajor_noswizzle(0, 128, 512);
-          constexpr uint32_t kALo = kPanelBytes >> 4, kBHi = Cfg::A_BYTES >> 4,
-                             kBLo = (Cfg::A_BYTES + kPanelBytes) >> 4;
-          const uint32_t base16 = (smem_base & 0x3ffff) >> 4;
-          uint32_t s = 0, ph = 0, tcount = 0, it = 0;
-          bool ok = true;
-          for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
-            for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-              if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
-                ok = false;
-                break;
-              }
-              pair_trace(p, 4, it);
-              if (kb == 0) {
-                if (!mbar_wait(smem_u32(&bar_corr_free), (tcount & 1) ^ 1, abortp, 32)) {
-                  ok = false;
-                  break;
-                }
-              }
-              tc_fence_after();
-              const uint32_t c16 = base16 + s * (Cfg::STAGE_BYTES >> 4);
-              if (!(p.debug_flags & 2)) {
-#pragma unroll
-              for (uint32_t j = 0; j < 2; ++j)
-                umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + kALo + 16 * j), dconst | (c16 + kBHi + 16 * j), idesc,
-                                    (kb == 0 && j == 0) ? 0u : 1u);
-#pragma unroll
-              for (uint32_t j = 0; j < 2; ++j)
-                umma_ss_pair<kTf32>(tmem_corr, dconst | (c16 + 16 * j), dconst | (c16 + kBLo + 16 * j), idesc, 1u);
-              }
-              umma_commit_pair(smem_u32(&bar_empty[s]));
-              if (++s == static_cast<uint32_t>(NST)) {
-                s = 0;
-                ph ^= 1;
-              }
-            }
-            if (!ok) break;
-            umma_commit_pair(smem_u32(&bar_corr_full));
-          }
-          if (!ok) {
-            abort_flag = 1;
-            atomicCAS(p.status, 0, kErrMmaWait);
-            umma_commit_pair(smem_u32(&bar_drain[1]));
-            mbar_wait_plain(smem_u32(&bar_drain[1]), 0);
-          }
+          if (!issue_corr_products<kTf32, true, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+                                                     abortp, p.debug_flags, nullptr))
+            mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
         }
       }
     }
@@ -286,19 +204,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           break;
         }
         tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_main + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-          if (c == 0) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] = __uint_as_float(v[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
-          }
-        }
+        promote_main_chunk<false>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(main_free_leader);
@@ -315,15 +221,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       const int col0 = tc.nt * BN + colbase;
       const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
       if constexpr (kEc) {
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_corr + lane_addr + colbase + cc * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v[i]) * corr_scale;
-        }
+        fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(corr_free_leader);
