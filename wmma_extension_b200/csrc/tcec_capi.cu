@@ -362,6 +362,7 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   fp.c_col_major = (lc == TCEC_COL_MAJOR);
   fp.status = st->status;
   fp.debug_flags = g_debug_flags;
+  fp.trace = g_trace;
   const long long ntiles = static_cast<long long>(fp.tiles_m) * fp.tiles_n * batch;
   const int grid = static_cast<int>(ntiles < st->sm_count ? ntiles : st->sm_count);
   if (policy_ec(policy))

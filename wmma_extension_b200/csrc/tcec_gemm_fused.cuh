@@ -59,6 +59,8 @@ struct GemmFusedParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;
+  unsigned long long* trace;  // development aid: hand-off timestamps of CTA 0, 6 roles x 4096 slots
+                              // (0 main saw full, 1 main chunk free, 2 landed, 3 converted, 4 corr saw full, 5 main committed)
   int debug_flags;  // timing experiments only (results invalid): bit 1 = no MMAs, bit 2 = no conversion, bit 3 = no stores
 };
 
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(640, 1)
     // ------------------------------------------------------------ converters
     setmaxnreg_dec<Cfg::REGS_CONVERT>();
     const int cw = warp - 12;
-    uint32_t s = 0, ph = 0;
+    uint32_t s = 0, ph = 0, cit = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.nkb; ++kb) {
@@ -198,6 +200,7 @@ __global__ void __launch_bounds__(640, 1)
           break;
         }
         mbar_try_wait(smem_u32(&bar_landed[s]), ph);  // each lane observes the completed phase itself
+        if (cw == 0 && lane == 0 && blockIdx.x == 0) trace_slot(p.trace, 2, cit);  // landed
         uint8_t* stage = smem_gen + s * Cfg::STAGE;
         // A: 16 groups or 4 boxes; B: 32 groups or 8 boxes.  Groups are dealt warp by warp, a box
         // goes to one warp (A's four boxes to every other warp).
@@ -217,6 +220,8 @@ __global__ void __launch_bounds__(640, 1)
         fence_proxy_async_smem();  // image written with ordinary stores, read by the tensor pipe
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_full[s]));
+        if (cw == 0 && lane == 0 && blockIdx.x == 0) trace_slot(p.trace, 3, cit);  // converted
+        ++cit;
         if (++s == static_cast<uint32_t>(NST)) {
           s = 0;
           ph ^= 1;
@@ -243,11 +248,11 @@ __global__ void __launch_bounds__(640, 1)
       const RingBarriers ring{bar_full, bar_empty};
       if (warp == 1) {
         if (!issue_main_products<false, false, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
-                                                    abortp, p.debug_flags, nullptr))
+                                                    abortp, p.debug_flags, blockIdx.x == 0 ? p.trace : nullptr))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
       } else {
         if (!issue_corr_products<false, false, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
-                                                    abortp, p.debug_flags, nullptr))
+                                                    abortp, p.debug_flags, blockIdx.x == 0 ? p.trace : nullptr))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
       }
     } else if (warp == 0 && lane == 0) {
