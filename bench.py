@@ -268,7 +268,8 @@ def run_ours(args):
     if dist_on:
         bufs = [torch.empty((args.panel_rows, k), dtype=torch.float32, device=device) for _ in range(2)] \
             if rank != 0 else None
-        ops = sharded.cuda_ops(policy)
+        # BENCH_FULL_SMEM=1 keeps the GEMM's full shared-memory footprint (A/B of the overlap with NCCL)
+        ops = sharded.cuda_ops(policy, beside_collectives=os.environ.get("BENCH_FULL_SMEM", "0") != "1")
 
         def step():
             sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=args.panel_rows, ops=ops,

@@ -188,6 +188,10 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                default: 4 % faster than one SM per tile at 4096^3 (389 vs 373 TFLOP/s) but it
  *                draws more power, and at the board's power cap it is slower (16384^3: 360 vs
  *                400 TFLOP/s, both at 990 W).
+ *   "store_turn" 1 (default) = the panel kernel turns its C stores through shared memory into full
+ *                128-byte lines and uses all 227 KB of the SM; 0 = direct stores and ~30 KB of
+ *                shared memory per SM left free, for callers whose communication kernels must
+ *                run beside the GEMM (the multi-GPU column-sharded driver sets it).
  *   "path"       0 = automatic; 1 = always split the operands into panels first, then multiply
  *                (two kernels; the faster one whenever the tensor pipe is the limit); 2 = use
  *                the single kernel that TMA-loads FP32 tiles and splits them in registers

@@ -165,6 +165,24 @@ def test_promotion_interval_option():
     assert errs[0] > 4 * errs[128]
 
 
+def test_direct_store_option_is_bit_identical():
+    """store_turn = 0 (direct stores, smaller shared-memory footprint) changes no result."""
+    rng = np.random.default_rng(5)
+    a = _t(rng.uniform(-1, 1, (300, 200)).astype(np.float32))
+    b = _t(rng.uniform(-1, 1, (200, 700)).astype(np.float32))
+    c0 = _t(rng.uniform(-1, 1, (300, 700)).astype(np.float32))
+    tcec.set_option("path", 1)
+    out = {}
+    try:
+        for turn in (1, 0):
+            tcec.set_option("store_turn", turn)
+            out[turn] = tcec.sgemm(a, b, c0.clone(), alpha=1.5, beta=-0.5)
+            tcec.device_status()
+    finally:
+        tcec.set_option("store_turn", 1)
+    assert torch.equal(out[0], out[1])
+
+
 def test_tile_width_option_gives_same_quality():
     rng = np.random.default_rng(34)
     a = rng.standard_normal((256, 512)).astype(np.float32)

@@ -72,6 +72,13 @@ def test_options_round_trip():
             tcec.set_option("tile_n", 96)
         with pytest.raises(tcec.TcecError):
             tcec.set_option("no_such_option", 1)
+        for name, default, other in (("cta_pair", 0, 1), ("path", 0, 2), ("store_turn", 1, 0), ("tile_n", 0, 128)):
+            assert tcec.get_option(name) == default
+            tcec.set_option(name, other)
+            assert tcec.get_option(name) == other
+            tcec.set_option(name, default)
+        with pytest.raises(tcec.TcecError):
+            tcec.set_option("store_turn", 2)
     finally:
         tcec.set_option("promote_k", old)
 

@@ -35,6 +35,7 @@ std::map<int, DeviceState> g_dev;
 int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
 int g_debug_flags = 0;
+int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
 int g_cta_pair = 0;  // 0: off, 1: CTA-pair kernel for 256-wide tiles when the problem is large enough
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
 unsigned long long* g_trace = nullptr;
@@ -190,7 +191,8 @@ void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
   using Cfg = GemmPanelCfg<BN, T, E>;
   const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * gp.batch;
   const int grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
-  tcec_gemm_panels_kernel<BN, T, E><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(gp);
+  tcec_gemm_panels_kernel<BN, T, E>
+      <<<grid, Cfg::THREADS, gp.store_turn ? Cfg::SMEM_BYTES : Cfg::SMEM_BYTES_NO_TURN, stream>>>(gp);
 }
 
 bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
@@ -259,6 +261,7 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
   gp.c_col_major = (lc == TCEC_COL_MAJOR);
   gp.status = st->status;
   gp.debug_flags = g_debug_flags;
+  gp.store_turn = g_store_turn;
   gp.trace = g_trace;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
   if (g_cta_pair && s.tile_n == 256 && m > 128) {
@@ -699,6 +702,11 @@ int tcec_set_option(const char* name, int value) {
     g_path = value;
     return TCEC_OK;
   }
+  if (!strcmp(name, "store_turn")) {
+    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
+    g_store_turn = value;
+    return TCEC_OK;
+  }
   if (!strcmp(name, "debug_flags")) {
     g_debug_flags = value;
     return TCEC_OK;
@@ -715,6 +723,22 @@ int tcec_get_option(const char* name, int* value) {
   }
   if (!strcmp(name, "tile_n")) {
     *value = g_tile_n;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "cta_pair")) {
+    *value = g_cta_pair;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "path")) {
+    *value = g_path;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "store_turn")) {
+    *value = g_store_turn;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "debug_flags")) {
+    *value = g_debug_flags;
     return TCEC_OK;
   }
   return TCEC_ERR_INVALID_ARGUMENT;

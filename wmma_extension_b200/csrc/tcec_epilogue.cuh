@@ -22,6 +22,12 @@ struct StoreTarget {
   float alpha, beta;
 };
 
+// alpha * v + beta * old with fixed rounding points (one product rounded, then one fused
+// multiply-add), so every store path of every kernel produces the same bits.
+__device__ __forceinline__ float axpby(float alpha, float v, float beta, float old) {
+  return __fmaf_rn(beta, old, __fmul_rn(alpha, v));
+}
+
 __device__ __forceinline__ void store_row_slice(const float (&acc)[128], int row, int col0, const StoreTarget& t) {
   if (row >= t.M) return;
 #pragma unroll
@@ -33,26 +39,25 @@ __device__ __forceinline__ void store_row_slice(const float (&acc)[128], int row
         const int col = col0 + cc * 32 + i;
         if (t.vec_ok && col + 3 < t.N) {
           float4 o;
-          o.x = t.alpha * acc[cc * 32 + i + 0];
-          o.y = t.alpha * acc[cc * 32 + i + 1];
-          o.z = t.alpha * acc[cc * 32 + i + 2];
-          o.w = t.alpha * acc[cc * 32 + i + 3];
           if (t.beta != 0.f) {
             const float4 old = *reinterpret_cast<const float4*>(crow + col);
-            o.x += t.beta * old.x;
-            o.y += t.beta * old.y;
-            o.z += t.beta * old.z;
-            o.w += t.beta * old.w;
+            o.x = axpby(t.alpha, acc[cc * 32 + i + 0], t.beta, old.x);
+            o.y = axpby(t.alpha, acc[cc * 32 + i + 1], t.beta, old.y);
+            o.z = axpby(t.alpha, acc[cc * 32 + i + 2], t.beta, old.z);
+            o.w = axpby(t.alpha, acc[cc * 32 + i + 3], t.beta, old.w);
+          } else {
+            o.x = __fmul_rn(t.alpha, acc[cc * 32 + i + 0]);
+            o.y = __fmul_rn(t.alpha, acc[cc * 32 + i + 1]);
+            o.z = __fmul_rn(t.alpha, acc[cc * 32 + i + 2]);
+            o.w = __fmul_rn(t.alpha, acc[cc * 32 + i + 3]);
           }
           *reinterpret_cast<float4*>(crow + col) = o;
         } else {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            if (col + e < t.N) {
-              float o = t.alpha * acc[cc * 32 + i + e];
-              if (t.beta != 0.f) o += t.beta * crow[col + e];
-              crow[col + e] = o;
-            }
+            if (col + e < t.N)
+              crow[col + e] = t.beta != 0.f ? axpby(t.alpha, acc[cc * 32 + i + e], t.beta, crow[col + e])
+                                            : __fmul_rn(t.alpha, acc[cc * 32 + i + e]);
           }
         }
       }
@@ -62,9 +67,7 @@ __device__ __forceinline__ void store_row_slice(const float (&acc)[128], int row
         const int col = col0 + cc * 32 + i;
         if (col < t.N) {
           float* dst = t.cbase + static_cast<long long>(col) * t.ldc + row;
-          float o = t.alpha * acc[cc * 32 + i];
-          if (t.beta != 0.f) o += t.beta * *dst;
-          *dst = o;
+          *dst = t.beta != 0.f ? axpby(t.alpha, acc[cc * 32 + i], t.beta, *dst) : __fmul_rn(t.alpha, acc[cc * 32 + i]);
         }
       }
     }
@@ -97,24 +100,22 @@ __device__ __forceinline__ void store_warp_block(const float (&acc)[128], int ro
       if (row < t.M) {
         float* dst = t.cbase + static_cast<long long>(row) * t.ldc + col;
         if (t.vec_ok && col + 3 < t.N) {
-          float4 o = make_float4(t.alpha * v0, t.alpha * v1, t.alpha * v2, t.alpha * v3);
+          float4 o;
           if (t.beta != 0.f) {
             const float4 old = *reinterpret_cast<const float4*>(dst);
-            o.x += t.beta * old.x;
-            o.y += t.beta * old.y;
-            o.z += t.beta * old.z;
-            o.w += t.beta * old.w;
+            o = make_float4(axpby(t.alpha, v0, t.beta, old.x), axpby(t.alpha, v1, t.beta, old.y),
+                            axpby(t.alpha, v2, t.beta, old.z), axpby(t.alpha, v3, t.beta, old.w));
+          } else {
+            o = make_float4(__fmul_rn(t.alpha, v0), __fmul_rn(t.alpha, v1), __fmul_rn(t.alpha, v2),
+                            __fmul_rn(t.alpha, v3));
           }
           *reinterpret_cast<float4*>(dst) = o;
         } else {
           const float v[4] = {v0, v1, v2, v3};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            if (col + e < t.N) {
-              float o = t.alpha * v[e];
-              if (t.beta != 0.f) o += t.beta * dst[e];
-              dst[e] = o;
-            }
+            if (col + e < t.N)
+              dst[e] = t.beta != 0.f ? axpby(t.alpha, v[e], t.beta, dst[e]) : __fmul_rn(t.alpha, v[e]);
           }
         }
       }

@@ -46,6 +46,8 @@ struct GemmPanelParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;             // device word; non-zero after a wait ran out
+  int store_turn;          // 1: stores go through the per-warp shared-memory buffers (launched with
+                           // SMEM_BYTES); 0: direct stores, launched with SMEM_BYTES_NO_TURN
   int debug_flags;         // timing experiments only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
   unsigned long long* trace;  // optional: CTA 0 writes clock64() at hand-off points (6 roles x 4096 slots)
 };
@@ -65,6 +67,7 @@ struct GemmPanelCfg {
   static constexpr int EPI_WARPS = 4 * NB;
   static constexpr int EPI_OFFSET = NST * STAGE_BYTES;   // epilogue turn buffers follow the ring
   static constexpr int SMEM_BYTES = NST * STAGE_BYTES + EPI_WARPS * kEpiBufBytes + 1024;
+  static constexpr int SMEM_BYTES_NO_TURN = NST * STAGE_BYTES + 1024;  // leaves ~30 KB of the SM to others
   static constexpr int TMEM_COLS = kEc ? 2 * BN : BN;  // 128, 256 or 512: powers of two
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   // 256-wide tiles run 384 threads (168 registers each at launch).  The control warpgroup needs
@@ -267,7 +270,11 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       st.vec_ok = vec_ok;
       st.alpha = p.alpha;
       st.beta = p.beta;
-      store_warp_block(acc, tc.mt * 128 + q * 32, col0, st, reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
+      if (p.store_turn)
+        store_warp_block(acc, tc.mt * 128 + q * 32, col0, st,
+                         reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
+      else
+        store_row_slice(acc, tc.mt * 128 + q * 32 + lane, col0, st);
     }
     if (!ok) {
       abort_flag = 1;

@@ -63,7 +63,10 @@ class LocalOps:
     gemm_panel: Callable[[torch.Tensor, object, torch.Tensor], None]  # (A panel, prepared B, C rows)
 
 
-def cuda_ops(policy: str = "fp16_ec") -> LocalOps:
+def cuda_ops(policy: str = "fp16_ec", beside_collectives: bool = False) -> LocalOps:
+    """Local compute through the CUDA library.  With ``beside_collectives`` the GEMM leaves
+    ~30 KB of shared memory per SM free (option ``store_turn`` = 0) so that the broadcast
+    kernel of the next row panel can run on the same SMs while the GEMM runs."""
     from . import tcec
 
     def prepare_b(b_local: torch.Tensor):
@@ -73,7 +76,13 @@ def cuda_ops(policy: str = "fp16_ec") -> LocalOps:
     def gemm_panel(a_panel: torch.Tensor, prepared, c_rows: torch.Tensor) -> None:
         b_packed, k, n = prepared
         a_packed = tcec.pack_a(a_panel, policy)
-        tcec.sgemm_packed(a_packed, b_packed, a_panel.shape[0], n, k, c_rows, policy=policy)
+        if beside_collectives:
+            tcec.set_option("store_turn", 0)
+        try:
+            tcec.sgemm_packed(a_packed, b_packed, a_panel.shape[0], n, k, c_rows, policy=policy)
+        finally:
+            if beside_collectives:
+                tcec.set_option("store_turn", 1)
 
     return LocalOps(prepare_b, gemm_panel)
 
@@ -91,7 +100,7 @@ def sgemm_column_sharded(a_root: Optional[torch.Tensor], b_local: torch.Tensor, 
     """
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
-    ops = ops or cuda_ops()
+    ops = ops or cuda_ops(beside_collectives=world > 1)
     if rank == root:
         if a_root is None or tuple(a_root.shape) != (m, k) or not a_root.is_contiguous():
             raise ValueError("root must pass a contiguous (m, k) matrix")
