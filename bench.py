@@ -37,6 +37,9 @@ METRIC = "tcec_sgemm_fp32_equiv_tflops"
 UNIT = "TFLOP/s"
 
 
+NCCL_CHANNELS = 4  # channels of the A broadcast at N > 1 = SMs kept out of the GEMM's grid
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -253,6 +256,10 @@ def run_ours(args):
     if dist_on:
         import torch.distributed as dist
         import datetime
+        # The broadcast moves 1 GiB per 21 ms step: a few channels carry it, and every channel is
+        # an SM the GEMM cannot use meanwhile.
+        os.environ.setdefault("NCCL_MAX_NCHANNELS", str(NCCL_CHANNELS))
+        os.environ.setdefault("NCCL_MIN_NCHANNELS", "1")
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     tcec.load()
     peaks = measured_peaks()
@@ -268,8 +275,7 @@ def run_ours(args):
     if dist_on:
         bufs = [torch.empty((args.panel_rows, k), dtype=torch.float32, device=device) for _ in range(2)] \
             if rank != 0 else None
-        # BENCH_FULL_SMEM=1 keeps the GEMM's full shared-memory footprint (A/B of the overlap with NCCL)
-        ops = sharded.cuda_ops(policy, beside_collectives=os.environ.get("BENCH_FULL_SMEM", "0") != "1")
+        ops = sharded.cuda_ops(policy, reserve_sms=int(os.environ.get("BENCH_RESERVE_SMS", str(NCCL_CHANNELS))))
 
         def step():
             sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=args.panel_rows, ops=ops,

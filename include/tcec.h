@@ -188,10 +188,13 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                default: 4 % faster than one SM per tile at 4096^3 (389 vs 373 TFLOP/s) but it
  *                draws more power, and at the board's power cap it is slower (16384^3: 360 vs
  *                400 TFLOP/s, both at 990 W).
+ *   "reserve_sms" 0..64 (default 0): SMs the panel GEMM does not occupy.  Its persistent CTAs take
+ *                every register of an SM, so a communication kernel launched beside it can only
+ *                run where the GEMM has no CTA; the column-sharded multi-GPU driver reserves as
+ *                many SMs as its broadcast uses channels.
  *   "store_turn" 1 (default) = the panel kernel turns its C stores through shared memory into full
  *                128-byte lines and uses all 227 KB of the SM; 0 = direct stores and ~30 KB of
- *                shared memory per SM left free, for callers whose communication kernels must
- *                run beside the GEMM (the multi-GPU column-sharded driver sets it).
+ *                shared memory per SM left free.
  *   "path"       0 = automatic; 1 = always split the operands into panels first, then multiply
  *                (two kernels; the faster one whenever the tensor pipe is the limit); 2 = use
  *                the single kernel that TMA-loads FP32 tiles and splits them in registers

@@ -36,6 +36,7 @@ int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
 int g_debug_flags = 0;
 int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
+int g_reserve_sms = 0;  // SMs the panel GEMM leaves idle (for a caller's communication kernels)
 int g_cta_pair = 0;  // 0: off, 1: CTA-pair kernel for 256-wide tiles when the problem is large enough
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
 unsigned long long* g_trace = nullptr;
@@ -190,7 +191,8 @@ template <int BN, bool T, bool E>
 void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
   using Cfg = GemmPanelCfg<BN, T, E>;
   const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * gp.batch;
-  const int grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
+  const int sms = sm_count - g_reserve_sms > 1 ? sm_count - g_reserve_sms : 1;
+  const int grid = static_cast<int>(ntiles < sms ? ntiles : sms);
   tcec_gemm_panels_kernel<BN, T, E>
       <<<grid, Cfg::THREADS, gp.store_turn ? Cfg::SMEM_BYTES : Cfg::SMEM_BYTES_NO_TURN, stream>>>(gp);
 }
@@ -707,6 +709,11 @@ int tcec_set_option(const char* name, int value) {
     g_store_turn = value;
     return TCEC_OK;
   }
+  if (!strcmp(name, "reserve_sms")) {
+    if (value < 0 || value > 64) return TCEC_ERR_INVALID_ARGUMENT;
+    g_reserve_sms = value;
+    return TCEC_OK;
+  }
   if (!strcmp(name, "debug_flags")) {
     g_debug_flags = value;
     return TCEC_OK;
@@ -735,6 +742,10 @@ int tcec_get_option(const char* name, int* value) {
   }
   if (!strcmp(name, "store_turn")) {
     *value = g_store_turn;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "reserve_sms")) {
+    *value = g_reserve_sms;
     return TCEC_OK;
   }
   if (!strcmp(name, "debug_flags")) {

@@ -63,10 +63,11 @@ class LocalOps:
     gemm_panel: Callable[[torch.Tensor, object, torch.Tensor], None]  # (A panel, prepared B, C rows)
 
 
-def cuda_ops(policy: str = "fp16_ec", beside_collectives: bool = False) -> LocalOps:
-    """Local compute through the CUDA library.  With ``beside_collectives`` the GEMM leaves
-    ~30 KB of shared memory per SM free (option ``store_turn`` = 0) so that the broadcast
-    kernel of the next row panel can run on the same SMs while the GEMM runs."""
+def cuda_ops(policy: str = "fp16_ec", reserve_sms: int = 0) -> LocalOps:
+    """Local compute through the CUDA library.  The GEMM's persistent CTAs take every register
+    of their SM, so a broadcast kernel launched beside it only runs where the GEMM has no CTA,
+    and a GEMM CTA that has to wait for such an SM delays the whole launch.  ``reserve_sms`` keeps
+    that many SMs out of the GEMM's grid (as many as the broadcast uses channels)."""
     from . import tcec
 
     def prepare_b(b_local: torch.Tensor):
@@ -76,13 +77,13 @@ def cuda_ops(policy: str = "fp16_ec", beside_collectives: bool = False) -> Local
     def gemm_panel(a_panel: torch.Tensor, prepared, c_rows: torch.Tensor) -> None:
         b_packed, k, n = prepared
         a_packed = tcec.pack_a(a_panel, policy)
-        if beside_collectives:
-            tcec.set_option("store_turn", 0)
+        if reserve_sms:
+            tcec.set_option("reserve_sms", reserve_sms)
         try:
             tcec.sgemm_packed(a_packed, b_packed, a_panel.shape[0], n, k, c_rows, policy=policy)
         finally:
-            if beside_collectives:
-                tcec.set_option("store_turn", 1)
+            if reserve_sms:
+                tcec.set_option("reserve_sms", 0)
 
     return LocalOps(prepare_b, gemm_panel)
 
@@ -100,7 +101,7 @@ def sgemm_column_sharded(a_root: Optional[torch.Tensor], b_local: torch.Tensor, 
     """
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
-    ops = ops or cuda_ops(beside_collectives=world > 1)
+    ops = ops or cuda_ops()
     if rank == root:
         if a_root is None or tuple(a_root.shape) != (m, k) or not a_root.is_contiguous():
             raise ValueError("root must pass a contiguous (m, k) matrix")
