@@ -212,7 +212,7 @@ def run_reference(args):
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": secs / max(1, len(times)) * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"sgemm M=N=K={size} row-major, U[-1,1); bounded row sample",
+            "config": {"workload": f"sgemm M=N=K={size} per GPU, FP32 row-major A,B, U[-1,1), alpha=1 beta=0",
                        "policy": "host FP64 check loop (the reference's CPU path)"},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
