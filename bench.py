@@ -262,6 +262,8 @@ def run_ours(args):
         os.environ.setdefault("NCCL_MIN_NCHANNELS", "1")
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     tcec.load()
+    if os.environ.get("BENCH_STATIC_TILES", "0") == "1":  # A/B switch for the tile order
+        tcec.set_option("static_tiles", 1)
     peaks = measured_peaks()
     size = args.size
     m = n = k = size

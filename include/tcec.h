@@ -192,6 +192,10 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                every register of an SM, so a communication kernel launched beside it can only
  *                run where the GEMM has no CTA; the column-sharded multi-GPU driver reserves as
  *                many SMs as its broadcast uses channels.
+ *   "static_tiles" 0 (default) = after the first wave the panel GEMM's CTAs draw their tiles from a
+ *                device-wide counter, so a CTA that gets its SM late (another kernel was running
+ *                there) processes fewer tiles instead of delaying the launch; 1 = static striding
+ *                (CTA i takes tiles i, i + grid, ...).  Same results bit for bit.
  *   "store_turn" 1 (default) = the panel kernel turns its C stores through shared memory into full
  *                128-byte lines and uses all 227 KB of the SM; 0 = direct stores and ~30 KB of
  *                shared memory per SM left free.

@@ -183,6 +183,34 @@ def test_direct_store_option_is_bit_identical():
     assert torch.equal(out[0], out[1])
 
 
+def test_tile_order_options_are_bit_identical():
+    """Tiles drawn from the device-wide counter, by static striding, and with SMs held back all
+    give the same bits; the counters are left at zero, so calls can follow one another."""
+    rng = np.random.default_rng(6)
+    a = _t(rng.uniform(-1, 1, (2000, 300)).astype(np.float32))
+    b = _t(rng.uniform(-1, 1, (300, 5000)).astype(np.float32))  # 16 x 20 = 320 tiles: more than two per SM
+    tcec.set_option("path", 1)
+    try:
+        tcec.set_option("static_tiles", 1)
+        ref = tcec.sgemm(a, b)
+        tcec.set_option("static_tiles", 0)
+        for _ in range(3):
+            assert torch.equal(tcec.sgemm(a, b), ref)
+        tcec.set_option("reserve_sms", 20)
+        assert torch.equal(tcec.sgemm(a, b), ref)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):  # a second stream has counters of its own
+            c2 = tcec.sgemm(a, b)
+        side.synchronize()
+        assert torch.equal(c2, ref)
+        tcec.device_status()
+    finally:
+        tcec.set_option("static_tiles", 0)
+        tcec.set_option("reserve_sms", 0)
+    exact = cpu.gemm_f64(a.cpu().numpy()[:64], b.cpu().numpy())
+    assert cpu.errors(ref[:64].cpu().numpy(), exact)["max_rel"] < 1e-6
+
+
 def test_tile_width_option_gives_same_quality():
     rng = np.random.default_rng(34)
     a = rng.standard_normal((256, 512)).astype(np.float32)

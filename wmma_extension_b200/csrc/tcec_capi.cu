@@ -28,6 +28,8 @@ struct DeviceState {
   int sm_count = 0;
   bool attrs_done = false;
   std::map<cudaStream_t, Workspace> ws;
+  std::map<cudaStream_t, unsigned int*> sched;  // per stream: the panel GEMM's two tile-scheduler counters
+  unsigned int* sched_fixed = nullptr;          // set instead by the allocation-free entry (a device symbol)
 };
 
 std::mutex g_mu;
@@ -36,6 +38,7 @@ int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
 int g_debug_flags = 0;
 int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
+int g_static_tiles = 0;  // 0: tiles beyond the first wave are drawn from a device-wide counter; 1: static striding
 int g_reserve_sms = 0;  // SMs the panel GEMM leaves idle (for a caller's communication kernels)
 int g_cta_pair = 0;  // 0: off, 1: CTA-pair kernel for 256-wide tiles when the problem is large enough
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
@@ -108,6 +111,25 @@ int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out
     w.bytes = bytes;
   }
   *out = w.ptr;
+  return TCEC_OK;
+}
+
+// Launches on one stream are ordered, so they can share one pair of counters (each launch leaves
+// them at zero); launches on different streams may overlap and get their own.
+int get_sched(DeviceState* st, cudaStream_t stream, unsigned int** out) {
+  if (st->sched_fixed) {
+    *out = st->sched_fixed;
+    return TCEC_OK;
+  }
+  unsigned int*& p = st->sched[stream];
+  if (!p) {
+    if (cudaMalloc(&p, 2 * sizeof(unsigned int)) != cudaSuccess) {
+      p = nullptr;
+      return TCEC_ERR_ALLOC;
+    }
+    TCEC_CUDA(cudaMemset(p, 0, 2 * sizeof(unsigned int)));
+  }
+  *out = p;
   return TCEC_OK;
 }
 
@@ -237,10 +259,10 @@ void pack_operand(bool k_contiguous, int rows, int k, const float* src, const fl
   }
 }
 
-void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t* panels_a,
+int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t* panels_a,
                  size_t a_stride, const uint8_t* panels_b, size_t b_stride, float beta, float* c,
                  float* const* c_array, long long ldc, long long stride_c, int lc, int batch,
-                 int policy, const DeviceState* st, cudaStream_t stream) {
+                 int policy, DeviceState* st, cudaStream_t stream) {
   GemmPanelParams gp{};
   gp.M = m;
   gp.N = n;
@@ -264,6 +286,10 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
   gp.status = st->status;
   gp.debug_flags = g_debug_flags;
   gp.store_turn = g_store_turn;
+  if (!g_static_tiles) {
+    const int rc = get_sched(st, stream, &gp.sched);
+    if (rc != TCEC_OK) return rc;
+  }
   gp.trace = g_trace;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
   if (g_cta_pair && s.tile_n == 256 && m > 128) {
@@ -280,7 +306,7 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
       tcec_gemm_panels_pair_kernel<false, true><<<grid, 384, GemmPairCfg<false, true>::SMEM_BYTES, stream>>>(gp);
     else
       tcec_gemm_panels_pair_kernel<false, false><<<grid, 384, GemmPairCfg<false, false>::SMEM_BYTES, stream>>>(gp);
-    return;
+    return TCEC_OK;
   }
 #define TCEC_DISPATCH(T, E)                                      \
   do {                                                           \
@@ -298,6 +324,7 @@ void gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t
   else
     TCEC_DISPATCH(false, false);
 #undef TCEC_DISPATCH
+  return TCEC_OK;
 }
 
 // ---------------------------------------------------------------- FP32-tile (fused) path
@@ -428,8 +455,9 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
                stream);
   pack_operand(lb == TCEC_COL_MAJOR, n, k, b, b_array, ldb, stride_b, batch, panels_b, s.b_bytes, policy,
                stream);
-  gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
-              lc, batch, policy, st, stream);
+  rc = gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
+                   lc, batch, policy, st, stream);
+  if (rc != TCEC_OK) return rc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
 }
@@ -522,8 +550,10 @@ int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, 
   pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbr, 0, policy, stream, neg);
   pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, first);
   pack_operand(b_kc, n, k, b, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, second);
-  gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbr, 0, 0.0f, prod_r, nullptr, inner, 0, lc, 1, policy, st, stream);
-  gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbi, 0, 0.0f, prod_i, nullptr, inner, 0, lc, 1, policy, st, stream);
+  rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbr, 0, 0.0f, prod_r, nullptr, inner, 0, lc, 1, policy, st, stream);
+  if (rc != TCEC_OK) return rc;
+  rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbi, 0, 0.0f, prod_i, nullptr, inner, 0, lc, 1, policy, st, stream);
+  if (rc != TCEC_OK) return rc;
   cgemm_combine_kernel<<<cgrid, 256, 0, stream>>>(prod_r, prod_i, reinterpret_cast<float2*>(c), ldc, inner,
                                                   outer, al, be, 1);
   TCEC_CUDA(cudaGetLastError());
@@ -611,8 +641,10 @@ int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0 || alpha == 0.f) return scale_only(beta, c, nullptr, ldc, 0, m, n, layout_c, 1, s);
   const Shape sh = plan(m, n, k, policy);
-  gemm_packed(sh, m, n, k, alpha, static_cast<const uint8_t*>(a_packed), 0,
-              static_cast<const uint8_t*>(b_packed), 0, beta, c, nullptr, ldc, 0, layout_c, 1, policy, st, s);
+  const int grc = gemm_packed(sh, m, n, k, alpha, static_cast<const uint8_t*>(a_packed), 0,
+                              static_cast<const uint8_t*>(b_packed), 0, beta, c, nullptr, ldc, 0, layout_c, 1,
+                              policy, st, s);
+  if (grc != TCEC_OK) return grc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
 }
@@ -714,6 +746,11 @@ int tcec_set_option(const char* name, int value) {
     g_reserve_sms = value;
     return TCEC_OK;
   }
+  if (!strcmp(name, "static_tiles")) {
+    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
+    g_static_tiles = value;
+    return TCEC_OK;
+  }
   if (!strcmp(name, "debug_flags")) {
     g_debug_flags = value;
     return TCEC_OK;
@@ -746,6 +783,10 @@ int tcec_get_option(const char* name, int* value) {
   }
   if (!strcmp(name, "reserve_sms")) {
     *value = g_reserve_sms;
+    return TCEC_OK;
+  }
+  if (!strcmp(name, "static_tiles")) {
+    *value = g_static_tiles;
     return TCEC_OK;
   }
   if (!strcmp(name, "debug_flags")) {
@@ -788,6 +829,9 @@ int tcec_destroy(void) {
     for (auto& w : kv.second.ws)
       if (w.second.ptr) cudaFree(w.second.ptr);
     kv.second.ws.clear();
+    for (auto& sc : kv.second.sched)
+      if (sc.second) cudaFree(sc.second);
+    kv.second.sched.clear();
     if (kv.second.status) cudaFree(kv.second.status);
     kv.second.status = nullptr;
     kv.second.attrs_done = false;
@@ -811,6 +855,7 @@ int tcec_destroy(void) {
 // the address is looked up once per device with cudaGetSymbolAddress, with that device current.
 static __device__ __align__(256) unsigned char g_static_panels[TCEC_STATIC_SCRATCH_BYTES];
 static __device__ int g_static_status_word;
+static __device__ unsigned int g_static_sched[2];  // the GEMM's tile-scheduler counters (zero between launches)
 
 namespace {
 constexpr int kMaxStaticDevices = 64;
@@ -818,6 +863,7 @@ struct StaticDevice {
   bool ready = false;
   uint8_t* panels = nullptr;
   int* status = nullptr;
+  unsigned int* sched = nullptr;
   int sm_count = 0;
 };
 StaticDevice g_static_dev[kMaxStaticDevices];  // fixed table: nothing is allocated on the host either
@@ -838,6 +884,9 @@ int static_device_state(StaticDevice** out) {
     p = nullptr;
     if (cudaGetSymbolAddress(&p, g_static_status_word) != cudaSuccess || p == nullptr) return TCEC_ERR_CUDA;
     sd.status = static_cast<int*>(p);
+    p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_sched) != cudaSuccess || p == nullptr) return TCEC_ERR_CUDA;
+    sd.sched = static_cast<unsigned int*>(p);
     // opting the kernels into their dynamic shared memory size changes a function attribute; it allocates nothing
     TCEC_CUDA((set_smem_attr<128, false, false>()));
     TCEC_CUDA((set_smem_attr<128, false, true>()));
@@ -891,8 +940,10 @@ int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, in
   DeviceState view;  // launch parameters only; owns nothing
   view.status = sd->status;
   view.sm_count = sd->sm_count;
-  gemm_packed(s, m, n, k, alpha, panels_a, 0, panels_b, 0, beta, c, nullptr, ldc, 0, layout_c, 1, policy, &view,
-              stream);
+  view.sched_fixed = sd->sched;
+  const int grc = gemm_packed(s, m, n, k, alpha, panels_a, 0, panels_b, 0, beta, c, nullptr, ldc, 0, layout_c, 1,
+                              policy, &view, stream);
+  if (grc != TCEC_OK) return grc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
 }

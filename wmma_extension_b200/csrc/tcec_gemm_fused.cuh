@@ -244,14 +244,15 @@ __global__ void __launch_bounds__(640, 1)
       im.b_hi16 = kBHi;
       im.b_lo16 = kBLo;
       im.idesc = umma_idesc(0u, 128, BN);
-      const TileWalk walk{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), ntiles, p.nkb, p.promo};
+      const StridedTiles tiles{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), ntiles};
+      const KWalk walk{p.nkb, p.promo};
       const RingBarriers ring{bar_full, bar_empty};
       if (warp == 1) {
-        if (!issue_main_products<false, false, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+        if (!issue_main_products<false, false, NST>(tiles, walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
                                                     abortp, p.debug_flags, blockIdx.x == 0 ? p.trace : nullptr))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
       } else {
-        if (!issue_corr_products<false, false, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+        if (!issue_corr_products<false, false, NST>(tiles, walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
                                                     abortp, p.debug_flags, blockIdx.x == 0 ? p.trace : nullptr))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
       }

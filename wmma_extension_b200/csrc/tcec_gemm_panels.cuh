@@ -46,6 +46,9 @@ struct GemmPanelParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;             // device word; non-zero after a wait ran out
+  unsigned int* sched;     // [0] tiles handed out beyond the first gridDim.x, [1] CTAs finished; both
+                           // zero between launches (the last CTA to finish resets them); null = static
+                           // striding (tile, tile + gridDim.x, ...)
   int store_turn;          // 1: stores go through the per-warp shared-memory buffers (launched with
                            // SMEM_BYTES); 0: direct stores, launched with SMEM_BYTES_NO_TURN
   int debug_flags;         // timing experiments only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
@@ -109,6 +112,8 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[NST], bar_empty[NST];
   __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain[2];
+  __shared__ uint64_t bar_tile_full[kTileRing], bar_tile_empty[kTileRing];
+  __shared__ int tile_ring[kTileRing];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_flag;
 
@@ -128,6 +133,10 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
     mbar_init(smem_u32(&bar_corr_free), Cfg::EPI_WARPS);
     mbar_init(smem_u32(&bar_drain[0]), 1);
     mbar_init(smem_u32(&bar_drain[1]), 1);
+    for (int i = 0; i < kTileRing; ++i) {
+      mbar_init(smem_u32(&bar_tile_full[i]), 1);
+      mbar_init(smem_u32(&bar_tile_empty[i]), (kEc ? 2 : 1) + Cfg::EPI_WARPS);  // MMA threads + epilogue warps
+    }
     abort_flag = 0;
     fence_mbar_init();
   }
@@ -150,8 +159,28 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       uint32_t it = 0, s = 0, ph = 0;
       uint32_t armed = 0, armed_parity = 0;  // per stage: a copy was issued, and in which phase
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      // Tile order: the first gridDim.x tiles by CTA index, the rest drawn from a device-wide
+      // counter, so a CTA that got its SM late (another kernel was there) takes fewer tiles
+      // instead of delaying the launch.  Every tile (and the end mark) is published to the
+      // CTA's other roles through the tile ring.
+      uint32_t tq = 0, tph = 0;
+      for (int tile = blockIdx.x; ok;) {
+        if (!mbar_wait(smem_u32(&bar_tile_empty[tq]), tph ^ 1, abortp, 64)) {
+          ok = false;
+          break;
+        }
+        tile_ring[tq] = tile < ntiles ? tile : kNoMoreTiles;
+        mbar_arrive(smem_u32(&bar_tile_full[tq]));
+        if (++tq == static_cast<uint32_t>(kTileRing)) {
+          tq = 0;
+          tph ^= 1;
+        }
+        if (tile >= ntiles) break;
         const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+        // The next tile is claimed late in this one (two ring fills before its end), so the claim
+        // follows the CTA's actual progress, and early enough for the atomic's latency to hide.
+        int next_tile = tile + static_cast<int>(gridDim.x);
+        const int claim_kb = p.nkb > 2 * NST ? p.nkb - 2 * NST : 0;
         const uint8_t* pa = p.panels_a + tc.b * p.panels_a_batch_stride +
                             static_cast<size_t>(tc.mt) * p.nkb * Cfg::A_BYTES;
         const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
@@ -161,6 +190,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
             ok = false;
             break;
           }
+          if (p.sched && kb == claim_kb) next_tile = static_cast<int>(gridDim.x + atomicAdd(&p.sched[0], 1u));
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
           if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {
@@ -180,6 +210,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
                         kPanelBytes, full);
           }
         }
+        tile = next_tile;
       }
       if (!ok) {
         abort_flag = 1;
@@ -200,15 +231,16 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       im.b_hi16 = Cfg::A_BYTES >> 4;
       im.b_lo16 = (Cfg::A_BYTES + Cfg::NB * kPanelBytes) >> 4;
       im.idesc = umma_idesc(kTf32 ? 2u : 0u, 128, BN);
-      const TileWalk walk{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), ntiles, p.nkb, p.promo};
+      RingTiles tiles{tile_ring, bar_tile_full, bar_tile_empty};
+      const KWalk walk{p.nkb, p.promo};
       const RingBarriers ring{bar_full, bar_empty};
       unsigned long long* trace = blockIdx.x == 0 ? p.trace : nullptr;
       if (warp == 1) {
-        if (!issue_main_products<kTf32, false, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+        if (!issue_main_products<kTf32, false, NST>(tiles, walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
                                                     abortp, p.debug_flags, trace))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
       } else {
-        if (!issue_corr_products<kTf32, false, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+        if (!issue_corr_products<kTf32, false, NST>(tiles, walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
                                                     abortp, p.debug_flags, trace))
           mma_thread_gave_up<false>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
       }
@@ -225,7 +257,14 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
     const bool vec_store = !p.c_col_major && (p.ldc % 4 == 0);
     uint32_t chunk = 0, tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+    RingTiles tiles{tile_ring, bar_tile_full, bar_tile_empty};
+    for (; ok; ++tcount) {
+      const int tile = tiles.next_warp(abortp);
+      if (tile == kNoMoreTiles) break;
+      if (tile == kTileWaitFailed) {
+        ok = false;
+        break;
+      }
       const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
       float acc[128];
@@ -285,6 +324,15 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base_s, Cfg::TMEM_COLS);
+  if (threadIdx.x == 0 && p.sched) {
+    // Every CTA has drawn its last tile by now; the last one out leaves the counters at zero.
+    __threadfence();
+    if (atomicAdd(&p.sched[1], 1u) == gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 }  // namespace tcec_sm100

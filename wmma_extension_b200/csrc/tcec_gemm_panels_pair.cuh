@@ -94,7 +94,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   im.b_hi16 = Cfg::A_BYTES >> 4;
   im.b_lo16 = (Cfg::A_BYTES + kPanelBytes) >> 4;
   im.idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
-  const TileWalk walk{pair, npairs, ntiles, p.nkb, p.promo};
+  const StridedTiles tiles{pair, npairs, ntiles};
+  const KWalk walk{p.nkb, p.promo};
   const RingBarriers ring{bar_full, bar_empty};
 
   if (warp < 4) {
@@ -167,7 +168,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           }
         } else {
           // -------------------------------------------------------- leader: main products
-          if (!issue_main_products<kTf32, true, NST>(walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
+          if (!issue_main_products<kTf32, true, NST>(tiles, walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
                                                      abortp, p.debug_flags, nullptr))
             mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
         }
@@ -176,7 +177,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       // ---------------------------------------------------------- leader: correction products
       if constexpr (kEc) {
         if (lane == 0 && leader) {
-          if (!issue_corr_products<kTf32, true, NST>(walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
+          if (!issue_corr_products<kTf32, true, NST>(tiles, walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
                                                      abortp, p.debug_flags, nullptr))
             mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
         }

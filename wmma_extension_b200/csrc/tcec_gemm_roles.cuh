@@ -23,11 +23,60 @@ struct OperandImage {
   uint32_t idesc;      // instruction descriptor (type, M, N)
 };
 
-// The tiles one CTA (or CTA pair) walks, and how K is cut.
-struct TileWalk {
-  int first, stride, ntiles;
+// How K is cut.
+struct KWalk {
   int nkb;    // K blocks per tile
   int promo;  // K blocks per promotion chunk; 0 = one chunk per tile
+};
+
+// Where a consumer role learns its next tile.  next() returns the tile index, kNoMoreTiles, or
+// kTileWaitFailed when a bounded wait ran out.
+enum : int { kNoMoreTiles = -1, kTileWaitFailed = -2 };
+
+// Static striding: tile, tile + stride, ...
+struct StridedTiles {
+  int tile, stride, ntiles;
+  __device__ __forceinline__ int next(volatile uint32_t*) {
+    if (tile >= ntiles) return kNoMoreTiles;
+    const int t = tile;
+    tile += stride;
+    return t;
+  }
+};
+
+// Tiles published by the CTA's producer thread through a small shared-memory ring (the producer
+// draws them from a device-wide counter, so a CTA that starts late simply processes fewer).
+// `empty` expects one arrive from every consumer: the MMA threads and each epilogue warp.
+constexpr int kTileRing = 4;
+struct RingTiles {
+  const volatile int* ring;
+  uint64_t* full;
+  uint64_t* empty;
+  uint32_t slot = 0, ph = 0;
+  // single-thread consumers
+  __device__ __forceinline__ int next(volatile uint32_t* abortp) {
+    if (!mbar_wait(smem_u32(&full[slot]), ph, abortp, 64)) return kTileWaitFailed;
+    const int t = ring[slot];
+    mbar_arrive(smem_u32(&empty[slot]));
+    advance();
+    return t;
+  }
+  // warp-collective consumers (all 32 lanes call it)
+  __device__ __forceinline__ int next_warp(volatile uint32_t* abortp) {
+    if (!mbar_wait_warp(smem_u32(&full[slot]), ph, abortp, 64)) return kTileWaitFailed;
+    mbar_try_wait(smem_u32(&full[slot]), ph);  // each lane observes the completed phase itself
+    const int t = ring[slot];
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&empty[slot]));
+    advance();
+    return t;
+  }
+  __device__ __forceinline__ void advance() {
+    if (++slot == static_cast<uint32_t>(kTileRing)) {
+      slot = 0;
+      ph ^= 1;
+    }
+  }
 };
 
 struct RingBarriers {
@@ -55,13 +104,17 @@ __device__ __forceinline__ void trace_slot(unsigned long long* trace, int role, 
 // instructions per MMA: descriptors are a constant OR-ed with a 14-bit address field, ring
 // positions and the promotion interval are counters.  Returns false when a bounded wait ran out.
 // debug_flags bit 1 (timing experiments only): issue no MMAs.
-template <bool kTf32, bool kPair, int NST>
-__device__ __forceinline__ bool issue_main_products(const TileWalk& w, const OperandImage& im, uint32_t tmem_main,
+template <bool kTf32, bool kPair, int NST, class TileSource>
+__device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWalk& w, const OperandImage& im,
+                                                    uint32_t tmem_main,
                                                     const RingBarriers& ring, uint64_t* bar_main_full,
                                                     uint64_t* bar_main_free, volatile uint32_t* abortp,
                                                     int debug_flags, unsigned long long* trace) {
   uint32_t it = 0, s = 0, ph = 0, chunk = 0;
-  for (int tile = w.first; tile < w.ntiles; tile += w.stride) {
+  for (;;) {
+    const int tile = tiles.next(abortp);
+    if (tile == kNoMoreTiles) break;
+    if (tile == kTileWaitFailed) return false;
     int left_in_chunk = 0;  // K blocks still to issue in the current chunk
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
@@ -98,13 +151,17 @@ __device__ __forceinline__ bool issue_main_products(const TileWalk& w, const Ope
 }
 
 // One thread: the correction products of every tile of the walk.
-template <bool kTf32, bool kPair, int NST>
-__device__ __forceinline__ bool issue_corr_products(const TileWalk& w, const OperandImage& im, uint32_t tmem_corr,
+template <bool kTf32, bool kPair, int NST, class TileSource>
+__device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWalk& w, const OperandImage& im,
+                                                    uint32_t tmem_corr,
                                                     const RingBarriers& ring, uint64_t* bar_corr_full,
                                                     uint64_t* bar_corr_free, volatile uint32_t* abortp,
                                                     int debug_flags, unsigned long long* trace) {
   uint32_t s = 0, ph = 0, tcount = 0, it = 0;
-  for (int tile = w.first; tile < w.ntiles; tile += w.stride, ++tcount) {
+  for (;; ++tcount) {
+    const int tile = tiles.next(abortp);
+    if (tile == kNoMoreTiles) break;
+    if (tile == kTileWaitFailed) return false;
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
       if (kb == 0) {
