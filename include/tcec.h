@@ -9,8 +9,9 @@
  * All matrix pointers are DEVICE pointers owned by the caller.  Calls are
  * asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default
  * stream) and return an integer status, never throw and never exit.  The
- * library owns only its cached workspace and a device status word, created on
- * first use per device and released by tcec_destroy().
+ * library owns only its cached workspace and two tile-scheduler counters per
+ * (device, stream) and a device status word, created on first use and released
+ * by tcec_destroy().
  *
  * The reference has no host API: its closest counterpart is the launch glue of
  * its batched example, launch_bgemm() (test/tcec/batch_gemm.cu:433-443) and the
