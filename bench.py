@@ -37,9 +37,6 @@ METRIC = "tcec_sgemm_fp32_equiv_tflops"
 UNIT = "TFLOP/s"
 
 
-NCCL_CHANNELS = 4  # channels of the A broadcast at N > 1 = SMs kept out of the GEMM's grid
-
-
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -256,10 +253,10 @@ def run_ours(args):
     if dist_on:
         import torch.distributed as dist
         import datetime
-        # The broadcast moves 1 GiB per 21 ms step: a few channels carry it, and every channel is
-        # an SM the GEMM cannot use meanwhile.
-        os.environ.setdefault("NCCL_MAX_NCHANNELS", str(NCCL_CHANNELS))
-        os.environ.setdefault("NCCL_MIN_NCHANNELS", "1")
+        # Tuning knobs for the overlap of the A broadcast with the GEMMs (defaults: NCCL's own channel
+        # count, no SMs held back; the GEMM's tile counter absorbs CTAs that start late):
+        # NCCL_MAX_NCHANNELS=c limits the broadcast to c CTAs, BENCH_RESERVE_SMS=r keeps r SMs out
+        # of the GEMM's grid for them.
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     tcec.load()
     if os.environ.get("BENCH_STATIC_TILES", "0") == "1":  # A/B switch for the tile order
@@ -277,7 +274,7 @@ def run_ours(args):
     if dist_on:
         bufs = [torch.empty((args.panel_rows, k), dtype=torch.float32, device=device) for _ in range(2)] \
             if rank != 0 else None
-        ops = sharded.cuda_ops(policy, reserve_sms=int(os.environ.get("BENCH_RESERVE_SMS", str(NCCL_CHANNELS))))
+        ops = sharded.cuda_ops(policy, reserve_sms=int(os.environ.get("BENCH_RESERVE_SMS", "0")))
 
         def step():
             sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=args.panel_rows, ops=ops,
