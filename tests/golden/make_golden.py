@@ -90,4 +90,4 @@ def main(outdir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    main(sys.argv[1] if len(sys.argv) > 1 else "golden_out")
