@@ -184,15 +184,16 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
  *                the reference's mma_rn_sync uses 16 or 8 (:640-706).
  *   "tile_n"     0 = automatic, 128 or 256.
- *   "cta_pair"   1 = run 256-wide tiles on pairs of SMs (tcgen05 cta_group::2: 256 x 256 tiles,
- *                each SM loads its rows of A and half of B).  Bit-identical results; off by
- *                default: 4 % faster than one SM per tile at 4096^3 (389 vs 373 TFLOP/s) but it
- *                draws more power, and at the board's power cap it is slower (16384^3: 360 vs
- *                400 TFLOP/s, both at 990 W).
+ *   "cta_pair"   256-wide tiles on pairs of SMs (tcgen05 cta_group::2: 256 x 256 tiles, each SM
+ *                loads its rows of A and half of B; bit-identical results).  -1 (default) = for
+ *                the policies without error correction, where one product per K block leaves the
+ *                kernel waiting on operands from L2 and the pair is 10-15 % faster (16384^3
+ *                fp16: 812 vs 677-735 TFLOP/s); 0 = never; 1 = whenever it applies.  With error
+ *                correction the pair is 4 % faster at 4096^3 but draws more power and is slower
+ *                at the board's power cap, so the automatic choice leaves it off there.
  *   "reserve_sms" 0..64 (default 0): SMs the panel GEMM does not occupy.  Its persistent CTAs take
  *                every register of an SM, so a communication kernel launched beside it can only
- *                run where the GEMM has no CTA; the column-sharded multi-GPU driver reserves as
- *                many SMs as its broadcast uses channels.
+ *                run where the GEMM has no CTA.
  *   "static_tiles" 0 (default) = after the first wave the panel GEMM's CTAs draw their tiles from a
  *                device-wide counter, so a CTA that gets its SM late (another kernel was running
  *                there) processes fewer tiles instead of delaying the launch; 1 = static striding

@@ -33,12 +33,12 @@ def _defaults():
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
-    tcec.set_option("cta_pair", 0)
+    tcec.set_option("cta_pair", -1)
     yield
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
-    tcec.set_option("cta_pair", 0)
+    tcec.set_option("cta_pair", -1)
 
 
 # ---------------------------------------------------------------- split (bit-exact)

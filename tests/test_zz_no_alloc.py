@@ -34,7 +34,8 @@ def test_static_entry_matches_the_allocating_one_twice_in_a_row():
     gen = torch.Generator(device=DEV)
     gen.manual_seed(90)
     # two different shapes back to back: the second call finds the first call's panels in the array
-    for (m, n, k, policy, alpha, beta) in [(384, 512, 1000, "fp16_ec", 1.0, 0.0), (200, 130, 70, "tf32_ec", 1.5, 0.5)]:
+    for (m, n, k, policy, alpha, beta) in [(384, 512, 1000, "fp16_ec", 1.0, 0.0), (200, 130, 70, "tf32_ec", 1.5, 0.5),
+                                             (300, 400, 200, "fp16_no_ec", 1.0, 0.0)]:
         a = torch.rand((m, k), generator=gen, device=DEV) * 2 - 1
         b = torch.rand((k, n), generator=gen, device=DEV) * 2 - 1
         c0 = torch.rand((m, n), generator=gen, device=DEV)
@@ -44,7 +45,8 @@ def test_static_entry_matches_the_allocating_one_twice_in_a_row():
         tcec.device_status()
         tcec.static_status()
         exact = alpha * (a.double() @ b.double()) + beta * c0.double()
-        tol = 1e-6 * exact.abs().max().item()  # the tolerance of the GEMM parity tests
+        # the tolerances of the GEMM parity tests (one product only without error correction)
+        tol = (2e-3 if policy.endswith("no_ec") else 1e-6) * exact.abs().max().item()
         assert (got.double() - want.double()).abs().max().item() <= tol
         assert (got.double() - exact).abs().max().item() <= tol
         assert torch.equal(got, want)  # same kernels on the same panels: not a bit differs

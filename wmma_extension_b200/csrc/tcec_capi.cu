@@ -40,7 +40,7 @@ int g_debug_flags = 0;
 int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
 int g_static_tiles = 0;  // 0: tiles beyond the first wave are drawn from a device-wide counter; 1: static striding
 int g_reserve_sms = 0;  // SMs the panel GEMM leaves idle (for a caller's communication kernels)
-int g_cta_pair = 0;  // 0: off, 1: CTA-pair kernel for 256-wide tiles when the problem is large enough
+int g_cta_pair = -1;  // -1: CTA-pair kernel for the policies without error correction; 0: never; 1: whenever it applies
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
 unsigned long long* g_trace = nullptr;
 
@@ -292,7 +292,10 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
   }
   gp.trace = g_trace;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
-  if (g_cta_pair && s.tile_n == 256 && m > 128) {
+  // One product per K block makes the kernel wait on operands from L2, which a CTA pair halves
+  // for B: measured 10-15 % faster there, and no faster (slower at the power cap) with three products.
+  const bool want_pair = g_cta_pair == 1 || (g_cta_pair == -1 && !ec);
+  if (want_pair && s.tile_n == 256 && m > 128) {
     // CTA pairs: 256 x 256 tiles, grid of up to sm_count/2 clusters of two CTAs
     gp.tiles_m = (m + 255) / 256;
     const long long npair_tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
@@ -727,7 +730,7 @@ int tcec_set_option(const char* name, int value) {
     return TCEC_OK;
   }
   if (!strcmp(name, "cta_pair")) {
-    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
+    if (value < -1 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
     g_cta_pair = value;
     return TCEC_OK;
   }
@@ -896,6 +899,14 @@ int static_device_state(StaticDevice** out) {
     TCEC_CUDA((set_smem_attr<256, false, true>()));
     TCEC_CUDA((set_smem_attr<256, true, false>()));
     TCEC_CUDA((set_smem_attr<256, true, true>()));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, false>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, false>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, true>::SMEM_BYTES));
+    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, true>::SMEM_BYTES));
     sd.ready = true;
   }
   *out = &sd;
