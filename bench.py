@@ -324,8 +324,8 @@ def run_ours(args):
         del ap, bp
         peak = peaks["bf16_sustained"] / 3.0
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                    "traffic": 1.133e9 * (size / 6144.0) ** 3,
-                    "traffic_is": "dram__bytes_read+write of this kernel captured by ncu at 6144^3 (1.133 GB per "
+                    "traffic": 1.126e9 * (size / 6144.0) ** 3,
+                    "traffic_is": "dram__bytes_read+write of this kernel captured by ncu at 6144^3 (1.126 GB per "
                                   "launch), scaled by (size/6144)^3; see profiles/",
                     "peak_is": f"dense 16-bit tensor peak / 3 products, sustained figure, {peaks['source']}",
                     "frac_of_burst_peak": achieved / (peaks["bf16_burst"] / 3.0),
