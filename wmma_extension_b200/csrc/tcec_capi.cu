@@ -36,13 +36,18 @@ std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
 int g_promote_k = -1;  // -1: chosen per call from K and the policy
 int g_tile_n = 0;
-int g_debug_flags = 0;
 int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
 int g_static_tiles = 0;  // 0: tiles beyond the first wave are drawn from a device-wide counter; 1: static striding
 int g_reserve_sms = 0;  // SMs the panel GEMM leaves idle (for a caller's communication kernels)
 int g_cta_pair = -1;  // -1: CTA-pair kernel for the policies without error correction; 0: never; 1: whenever it applies
 int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
-unsigned long long* g_trace = nullptr;
+#ifdef TCEC_DEVELOP
+int g_debug_flags = 0;               // switches that leave out parts of a kernel (results invalid)
+unsigned long long* g_trace = nullptr;  // device buffer for hand-off timestamps
+#else
+constexpr int g_debug_flags = 0;
+constexpr unsigned long long* g_trace = nullptr;
+#endif
 
 #define TCEC_CUDA(call)                        \
   do {                                         \
@@ -709,12 +714,15 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
   return TCEC_OK;
 }
 
-// Development aid, not part of the declared ABI: device buffer of 6 * 4096 u64 for hand-off timestamps.
+#ifdef TCEC_DEVELOP
+// Develop builds only (not part of the declared ABI): device buffer of kTraceRoles * 4096 u64 for
+// hand-off timestamps.
 int tcec_debug_set_trace(unsigned long long* dev_buffer) {
   std::lock_guard<std::mutex> lock(g_mu);
   g_trace = dev_buffer;
   return TCEC_OK;
 }
+#endif
 
 int tcec_set_option(const char* name, int value) {
   if (!name) return TCEC_ERR_INVALID_ARGUMENT;
@@ -754,10 +762,12 @@ int tcec_set_option(const char* name, int value) {
     g_static_tiles = value;
     return TCEC_OK;
   }
+#ifdef TCEC_DEVELOP
   if (!strcmp(name, "debug_flags")) {
     g_debug_flags = value;
     return TCEC_OK;
   }
+#endif
   return TCEC_ERR_INVALID_ARGUMENT;
 }
 
@@ -792,10 +802,12 @@ int tcec_get_option(const char* name, int* value) {
     *value = g_static_tiles;
     return TCEC_OK;
   }
+#ifdef TCEC_DEVELOP
   if (!strcmp(name, "debug_flags")) {
     *value = g_debug_flags;
     return TCEC_OK;
   }
+#endif
   return TCEC_ERR_INVALID_ARGUMENT;
 }
 

@@ -59,9 +59,11 @@ struct GemmFusedParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;
-  unsigned long long* trace;  // development aid: hand-off timestamps of CTA 0, 6 roles x 4096 slots
-                              // (0 main saw full, 1 main chunk free, 2 landed, 3 converted, 4 corr saw full, 5 main committed)
-  int debug_flags;  // timing experiments only (results invalid): bit 1 = no MMAs, bit 2 = no conversion, bit 3 = no stores
+  unsigned long long* trace;  // develop builds only: hand-off timestamps of CTA 0, rows of 4096 slots
+                              // (0 main saw full, 1 main chunk free, 2 landed, 3 converted, 4 corr saw full,
+                              //  5 main committed, 6 epilogue: chunk seen / drained, 7 epilogue: corr seen /
+                              //  folded / stored, 8 producer: stage issued)
+  int debug_flags;  // develop builds only (results invalid): bit 1 = no MMAs, bit 2 = no conversion, bit 3 = no stores
 };
 
 template <bool kEc>
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(640, 1)
         uint8_t* stage = smem_gen + s * Cfg::STAGE;
         // A: 16 groups or 4 boxes; B: 32 groups or 8 boxes.  Groups are dealt warp by warp, a box
         // goes to one warp (A's four boxes to every other warp).
-        if (p.debug_flags & 4) {
+        if (dev_flag(p.debug_flags, 4)) {
         } else {
           if (p.a_k_contiguous) {
             convert_groups_inplace<kEc, 2>(stage + cw * 1024, 8192, lane);
@@ -259,6 +261,7 @@ __global__ void __launch_bounds__(640, 1)
     } else if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer
       uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0;
+      [[maybe_unused]] uint32_t pit = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
@@ -270,6 +273,7 @@ __global__ void __launch_bounds__(640, 1)
           const uint32_t landed = smem_u32(&bar_landed[s]);
           const uint32_t dst = smem_base + s * Cfg::STAGE;
           mbar_arrive_expect_tx(landed, Cfg::STAGE);
+          if (blockIdx.x == 0) trace_slot(p.trace, 8, pit++);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
           if (p.a_k_contiguous) {
@@ -307,6 +311,7 @@ __global__ void __launch_bounds__(640, 1)
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     uint32_t chunk = 0, tcount = 0;
     bool ok = true;
+    const bool etrace = (warp == 4 && lane == 0 && blockIdx.x == 0);
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
       const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
@@ -316,11 +321,13 @@ __global__ void __launch_bounds__(640, 1)
           ok = false;
           break;
         }
+        if (etrace) trace_slot(p.trace, 6, 2 * chunk);
         tc_fence_after();
         promote_main_chunk<false>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_main_free));
+        if (etrace) trace_slot(p.trace, 6, 2 * chunk + 1);
       }
       if (!ok) break;
       if constexpr (kEc) {
@@ -328,11 +335,13 @@ __global__ void __launch_bounds__(640, 1)
           ok = false;
           break;
         }
+        if (etrace) trace_slot(p.trace, 7, 3 * tcount);
         tc_fence_after();
         fold_correction(acc, tmem_corr + lane_addr + colbase, 1.0f / 2048.0f);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));
+        if (etrace) trace_slot(p.trace, 7, 3 * tcount + 1);
       }
       StoreTarget st;
       st.cbase = p.c + tc.b * p.c_batch_stride;
@@ -343,9 +352,10 @@ __global__ void __launch_bounds__(640, 1)
       st.vec_ok = !p.c_col_major && (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(st.cbase) & 15) == 0);
       st.alpha = p.alpha;
       st.beta = p.beta;
-      if (!(p.debug_flags & 8))
+      if (!dev_flag(p.debug_flags, 8))
         store_warp_block(acc, tc.mt * 128 + q * 32, tc.nt * BN + colbase, st,
                          reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
+      if (etrace) trace_slot(p.trace, 7, 3 * tcount + 2);
     }
     if (!ok) {
       abort_flag = 1;

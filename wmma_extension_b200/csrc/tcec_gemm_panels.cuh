@@ -51,8 +51,8 @@ struct GemmPanelParams {
                            // striding (tile, tile + gridDim.x, ...)
   int store_turn;          // 1: stores go through the per-warp shared-memory buffers (launched with
                            // SMEM_BYTES); 0: direct stores, launched with SMEM_BYTES_NO_TURN
-  int debug_flags;         // timing experiments only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
-  unsigned long long* trace;  // optional: CTA 0 writes clock64() at hand-off points (6 roles x 4096 slots)
+  int debug_flags;         // develop builds only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
+  unsigned long long* trace;  // develop builds only: CTA 0 writes clock64() at hand-off points
 };
 
 enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3 };
@@ -84,7 +84,7 @@ struct GemmPanelCfg {
 };
 
 __device__ __forceinline__ void trace_mark(const GemmPanelParams& p, int role, uint32_t idx) {
-  if (p.trace && blockIdx.x == 0 && idx < 4096) p.trace[role * 4096 + idx] = clock64();
+  if (blockIdx.x == 0) trace_slot(p.trace, role, idx);
 }
 struct TileCoord {
   int b, mt, nt;
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
           if (p.sched && kb == claim_kb) next_tile = static_cast<int>(gridDim.x + atomicAdd(&p.sched[0], 1u));
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
-          if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {
+          if (dev_flag(p.debug_flags, 1) && it >= static_cast<uint32_t>(NST)) {
             mbar_arrive(full);
             continue;
           }

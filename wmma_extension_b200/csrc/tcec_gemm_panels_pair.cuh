@@ -115,7 +115,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
               ok = false;
               break;
             }
-            if ((p.debug_flags & 1) && it >= static_cast<uint32_t>(NST)) {  // timing experiment: no loads
+            if (dev_flag(p.debug_flags, 1) && it >= static_cast<uint32_t>(NST)) {  // develop builds: no loads
               mbar_arrive(smem_u32(&bar_full[s]));
               if (++s == static_cast<uint32_t>(NST)) {
                 s = 0;

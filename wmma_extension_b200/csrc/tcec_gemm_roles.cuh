@@ -95,15 +95,24 @@ __device__ __forceinline__ void umma_commit_to(uint32_t bar) {
   else umma_commit(bar);
 }
 
-// Optional hand-off timestamps (development aid): `trace` is null except in the CTA that records.
+// Development aids exist only in builds with -DTCEC_DEVELOP: switches that leave out parts of a
+// kernel for timing experiments (results invalid) and hand-off timestamps (`trace` is null except
+// in the CTA that records; kTraceRoles rows of 4096 slots).  The default build compiles both away.
+constexpr int kTraceRoles = 12;
+#ifdef TCEC_DEVELOP
+__device__ __forceinline__ bool dev_flag(int flags, int bit) { return (flags & bit) != 0; }
 __device__ __forceinline__ void trace_slot(unsigned long long* trace, int role, uint32_t idx) {
   if (trace && idx < 4096) trace[role * 4096 + idx] = clock64();
 }
+#else
+__device__ __forceinline__ constexpr bool dev_flag(int, int) { return false; }
+__device__ __forceinline__ void trace_slot(unsigned long long*, int, uint32_t) {}
+#endif
 
 // One thread: the main products of every tile of the walk.  Kept to a handful of integer
 // instructions per MMA: descriptors are a constant OR-ed with a 14-bit address field, ring
 // positions and the promotion interval are counters.  Returns false when a bounded wait ran out.
-// debug_flags bit 1 (timing experiments only): issue no MMAs.
+// Develop builds only: debug_flags bit 1 issues no MMAs.
 template <bool kTf32, bool kPair, int NST, class TileSource>
 __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWalk& w, const OperandImage& im,
                                                     uint32_t tmem_main,
@@ -129,7 +138,7 @@ __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWal
       }
       tc_fence_after();
       const uint32_t a16 = im.base16 + s * im.stage16;
-      if (!(debug_flags & 2)) {
+      if (!dev_flag(debug_flags, 2)) {
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_main, im.dconst | (a16 + 16 * j), im.dconst | (a16 + im.b_hi16 + 16 * j),
@@ -171,7 +180,7 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
       trace_slot(trace, 4, it);
       tc_fence_after();
       const uint32_t c16 = im.base16 + s * im.stage16;
-      if (!(debug_flags & 2)) {
+      if (!dev_flag(debug_flags, 2)) {
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_corr, im.dconst | (c16 + im.a_lo16 + 16 * j),
