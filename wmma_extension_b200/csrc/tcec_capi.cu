@@ -364,6 +364,20 @@ bool encode_operand_map(CUtensorMap* map, const float* base, bool k_contiguous, 
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map of a row-major C for tensor stores: 32 x 32 boxes, 128-byte swizzle (the layout the
+// epilogue writes its store boxes in).  Elements of a box outside the matrix are not written.
+bool encode_c_map(CUtensorMap* map, float* base, int m, int n, long long ldc, long long batch_stride, int batch) {
+  if (!g_encode) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ldc) * 4,
+                           static_cast<cuuint64_t>(batch > 1 ? batch_stride : ldc * static_cast<long long>(m)) * 4};
+  cuuint32_t box[3] = {32u, 32u, 1u};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool tma_addressable(const float* base, long long ld, long long stride, int batch) {
   return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ld % 4 == 0 && (batch <= 1 || stride % 4 == 0) &&
          ld < (1ll << 36) && stride < (1ll << 36);
@@ -380,16 +394,21 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   if (!wanted) return false;
   if (!tma_addressable(a, lda, stride_a, batch) || !tma_addressable(b, ldb, stride_b, batch)) return false;
   const bool a_kc = (la == TCEC_ROW_MAJOR), b_kc = (lb == TCEC_COL_MAJOR);
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
   if (!encode_operand_map(&map_a, a, a_kc, m, k, lda, stride_a, batch, 128)) return false;
-  if (!encode_operand_map(&map_b, b, b_kc, n, k, ldb, stride_b, batch, 256)) return false;
+  if (!encode_operand_map(&map_b, b, b_kc, n, k, ldb, stride_b, batch, 128)) return false;
+  // C goes out through tensor stores when nothing has to be read back and its rows are addressable.
+  const bool c_tma = lc == TCEC_ROW_MAJOR && beta == 0.f && tma_addressable(c, ldc, stride_c, batch) &&
+                     encode_c_map(&map_c, c, m, n, ldc, stride_c, batch);
+  if (!c_tma) map_c = map_a;  // unused by the kernel
   GemmFusedParams fp{};
+  fp.c_tma = c_tma ? 1 : 0;
   fp.M = m;
   fp.N = n;
   fp.K = k;
   fp.batch = batch;
   fp.nkb = (k + 31) / 32;
-  fp.tiles_m = (m + 127) / 128;
+  fp.tiles_m = (m + 255) / 256;  // 256 x 256 tiles on CTA pairs
   fp.tiles_n = (n + 255) / 256;
   fp.promo = promote_blocks(k, policy, 32);
   fp.a_k_contiguous = a_kc;
@@ -404,11 +423,12 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   fp.debug_flags = g_debug_flags;
   fp.trace = g_trace;
   const long long ntiles = static_cast<long long>(fp.tiles_m) * fp.tiles_n * batch;
-  const int grid = static_cast<int>(ntiles < st->sm_count ? ntiles : st->sm_count);
+  const int max_pairs = st->sm_count / 2;
+  const int grid = 2 * static_cast<int>(ntiles < max_pairs ? ntiles : max_pairs);
   if (policy_ec(policy))
-    tcec_gemm_fused_kernel<true><<<grid, GemmFusedCfg<true>::THREADS, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+    tcec_gemm_fused_kernel<true><<<grid, GemmFusedCfg<true>::THREADS, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b, map_c);
   else
-    tcec_gemm_fused_kernel<false><<<grid, GemmFusedCfg<false>::THREADS, GemmFusedCfg<false>::SMEM_BYTES, stream>>>(fp, map_a, map_b);
+    tcec_gemm_fused_kernel<false><<<grid, GemmFusedCfg<false>::THREADS, GemmFusedCfg<false>::SMEM_BYTES, stream>>>(fp, map_a, map_b, map_c);
   return true;
 }
 

@@ -254,6 +254,45 @@ __device__ __forceinline__ void promote_main_chunk(float (&acc)[128], uint32_t t
   }
 }
 
+// The same two steps for kernels whose epilogue has a smaller register share (128 sums + 32
+// temporaries).  A tile's first chunk is loaded straight into the sums with one wait; later chunks
+// and the correction term come in pairs of 16-column loads, both in flight before the one wait
+// (a TMEM load costs ~200 cycles whatever its width, so what counts is how many waits there are).
+__device__ __forceinline__ void promote_main_chunk_narrow(float (&acc)[128], uint32_t taddr, bool first) {
+  if (first) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32b_x32_f(taddr + cc * 32, &acc[cc * 32]);
+    tmem_ld_wait();
+  } else {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      uint32_t v0[16], v1[16];
+      tmem_ld_32x32b_x16(taddr + cc * 32, v0);
+      tmem_ld_32x32b_x16(taddr + cc * 32 + 16, v1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        acc[cc * 32 + i] += __uint_as_float(v0[i]);
+        acc[cc * 32 + 16 + i] += __uint_as_float(v1[i]);
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fold_correction_narrow(float (&acc)[128], uint32_t taddr, float scale) {
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t v0[16], v1[16];
+    tmem_ld_32x32b_x16(taddr + cc * 32, v0);
+    tmem_ld_32x32b_x16(taddr + cc * 32 + 16, v1);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      acc[cc * 32 + i] = acc[cc * 32 + i] + __uint_as_float(v0[i]) * scale;
+      acc[cc * 32 + 16 + i] = acc[cc * 32 + 16 + i] + __uint_as_float(v1[i]) * scale;
+    }
+  }
+}
+
 // Epilogue thread: out = main + corr * scale (tcec.hpp:332-336; scale = 2^-11 for fp16, 1 for tf32).
 __device__ __forceinline__ void fold_correction(float (&acc)[128], uint32_t taddr, float scale) {
 #pragma unroll
