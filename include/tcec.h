@@ -35,6 +35,7 @@ extern "C" {
 #define TCEC_ERR_TIMEOUT 4 /* a bounded device-side wait ran out */
 #define TCEC_ERR_ALLOC 5
 #define TCEC_ERR_TOO_LARGE 6 /* tcec_sgemm_static only: operands exceed TCEC_STATIC_SCRATCH_BYTES */
+#define TCEC_ERR_COMM 7 /* the communication library (NCCL) is missing, failed, or no communicator exists */
 
 /* storage order of a matrix: element (i,j) at i*ld + j (row) or i + j*ld (col) */
 #define TCEC_ROW_MAJOR 0
@@ -130,6 +131,71 @@ size_t tcec_static_scratch_bytes(void);
 int tcec_static_status(int* detail);
 
 /*
+ * tcec_sgemm on HOST operands (pinned memory makes the copies asynchronous): B is copied in and
+ * split once, A travels in panels of `panel_rows` rows (0 = 2048), and the copy-in of panel p+1,
+ * the GEMM on panel p and the copy-out of panel p-1 overlap on three streams.  The call returns
+ * once everything is queued; the result is complete when `stream` has reached the end of the
+ * call's work (synchronise it, or record an event on it, before reading c_host).  The reference
+ * example stages its operands with one cudaMemcpy each before and after the launch
+ * (test/tcec/batch_gemm.cu:515-533, :548); this is that sequence pipelined.  Device staging
+ * buffers are library-owned and cached per device; one such call at a time per device.
+ */
+int tcec_sgemm_host(int layout_a, int layout_b, int layout_c, int m, int n, int k, float alpha,
+                    const float* a_host, long long lda, const float* b_host, long long ldb, float beta,
+                    float* c_host, long long ldc, int policy, int panel_rows, void* stream);
+
+/*
+ * Several GPUs of one box.  K is never split, so there is no reduction: a batch is divided by
+ * matrices (no collective at all), a large GEMM by column blocks of B and C with A broadcast
+ * from its owner by NCCL (ncclBroadcast of split row panels, each panel's flag raised behind it;
+ * one persistent GEMM launch per GPU consumes the panels as they arrive and leaves "comm_sms"
+ * SMs to the broadcast).  The reference has no multi-GPU code and no collective call site; these
+ * entries stand where its launch glue does (test/tcec/batch_gemm.cu:433-443).  NCCL is loaded at
+ * run time (libnccl.so.2, or the library named by TCEC_NCCL_LIBRARY / tcec_comm_set_library),
+ * so single-GPU users need none.  Kernels only read their own GPU's memory.
+ *
+ * One process drives all devices: tcec_sgemm_multi / tcec_sgemm_batched_multi take a device
+ * list; operand i lives on devices[i]; A (m x k) lives on devices[0]; streams may be NULL (the
+ * default stream of each device) or one stream per device.  Communicators for the list are made
+ * on first use and freed by tcec_destroy().  The calls return when everything is queued; the
+ * first status that is not TCEC_OK among the devices is returned.
+ *   n_local[i]  columns of B and C held by devices[i] (whole output tiles of 256 columns keep
+ *               every GPU's work even); b[i] is k x n_local[i], c[i] is m x n_local[i].
+ */
+int tcec_sgemm_multi(int ndev, const int* devices, int layout_a, int layout_b, int layout_c, int m,
+                     const int* n_local, int k, float alpha, const float* a, long long lda,
+                     const float* const* b, const long long* ldb, float beta, float* const* c,
+                     const long long* ldc, int policy, void* const* streams);
+int tcec_sgemm_batched_multi(int ndev, const int* devices, int layout_a, int layout_b, int layout_c, int m, int n,
+                             int k, float alpha, const float* const* a, long long lda, long long stride_a,
+                             const float* const* b, long long ldb, long long stride_b, float beta,
+                             float* const* c, long long ldc, long long stride_c, const int* batch_local,
+                             int policy, void* const* streams);
+
+/*
+ * One process per device (what torchrun and MPI launchers give): rank 0 obtains an id with
+ * tcec_comm_unique_id, hands its TCEC_COMM_ID_BYTES bytes to the other ranks by whatever means
+ * the job has, and every rank calls tcec_comm_init_rank with its device current.  Then
+ * tcec_sgemm_column_shard is this rank's part of the column-sharded GEMM: `a` is read on `root`
+ * only; b (k x n_local) and c (m x n_local) are this rank's blocks.  Every rank must call it, in
+ * the same order.  The _host form takes host operands (A on the root, B and C blocks on every
+ * rank) and pipelines copy-in, broadcast, GEMM and copy-out in panels of `panel_rows` rows.
+ * Without a communicator (or with one rank) both forms compute locally.
+ */
+#define TCEC_COMM_ID_BYTES 128
+int tcec_comm_set_library(const char* path);
+int tcec_comm_unique_id(void* id);
+int tcec_comm_init_rank(int nranks, int rank, const void* id);
+int tcec_comm_destroy(void);
+int tcec_sgemm_column_shard(int root, int layout_a, int layout_b, int layout_c, int m, int n_local, int k,
+                            float alpha, const float* a, long long lda, const float* b, long long ldb, float beta,
+                            float* c, long long ldc, int policy, void* stream);
+int tcec_sgemm_column_shard_host(int root, int layout_a, int layout_b, int layout_c, int m, int n_local, int k,
+                                 float alpha, const float* a_host, long long lda, const float* b_host,
+                                 long long ldb, float beta, float* c_host, long long ldc, int policy,
+                                 int panel_rows, void* stream);
+
+/*
  * Split once, multiply many times.  tcec_pack_a / tcec_pack_b run the split of
  * load_matrix_sync (include/wmma_extension/tcec/tcec.hpp:194-236) over a whole
  * operand and store hi (+ scaled lo) in the layout the GEMM kernel streams;
@@ -138,8 +204,9 @@ int tcec_static_status(int* detail);
  * aligned, where rows = m for A and n for B.  The reference re-splits a tile in
  * every warp that consumes it (test/tcec/batch_gemm.cu:232-255); packing is what
  * lets one operand (B of a column shard, A after its broadcast) be split once.
- * A row sub-range of a packed operand that starts at a multiple of 128 rows is
- * itself a packed operand: it begins tcec_packed_row_offset(row, k, policy) bytes in.
+ * A row sub-range of a packed operand that starts at a multiple of 256 rows is
+ * itself a packed operand: it begins tcec_packed_row_offset(row, k, policy) bytes in
+ * (0 for any other row: the 256-wide tiles and the CTA-pair kernel read row blocks in pairs).
  */
 size_t tcec_packed_bytes(int rows, int k, int policy);
 size_t tcec_packed_row_offset(int row, int k, int policy);
@@ -191,9 +258,15 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                fp16: 812 vs 677-735 TFLOP/s); 0 = never; 1 = whenever it applies.  With error
  *                correction the pair is 4 % faster at 4096^3 but draws more power and is slower
  *                at the board's power cap, so the automatic choice leaves it off there.
- *   "reserve_sms" 0..64 (default 0): SMs the panel GEMM does not occupy.  Its persistent CTAs take
- *                every register of an SM, so a communication kernel launched beside it can only
+ *   "reserve_sms" 0..64 (default 0): SMs the GEMM kernels do not occupy.  Their persistent CTAs take
+ *                every register of an SM, so a communication kernel launched beside them can only
  *                run where the GEMM has no CTA.
+ *   "comm_sms"   1..64 (default 8): SMs the column-sharded step leaves to the broadcast of A; also
+ *                the limit on the broadcast's CTAs (read when a communicator is created).
+ *   "comm_panel_rows" rows of A per broadcast in the column-sharded step (default 2048, a multiple
+ *                of 256).
+ *   "comm_helper" 1 (default) = once the broadcast is over, a second GEMM launch that shares the
+ *                first one's tile counter takes the SMs it had; 0 = they stay idle.
  *   "static_tiles" 0 (default) = after the first wave the panel GEMM's CTAs draw their tiles from a
  *                device-wide counter, so a CTA that gets its SM late (another kernel was running
  *                there) processes fewer tiles instead of delaying the launch; 1 = static striding

@@ -451,11 +451,40 @@ def test_packed_entry_points_match_plain_call():
     want = tcec.sgemm(at, bt)
     ap, bp = tcec.pack_a(at), tcec.pack_b(bt)
     assert torch.equal(tcec.sgemm_packed(ap, bp, m, n, k), want)
-    # a row sub-range of packed A is itself a packed A
-    off = tcec.packed_row_offset(128, k)
-    part = tcec.sgemm_packed(ap[off:], bp, m - 128, n, k)
-    assert torch.equal(part, want[128:])
+    # a row sub-range of packed A that starts at a multiple of 256 rows is itself a packed A
+    off = tcec.packed_row_offset(256, k)
+    part = tcec.sgemm_packed(ap[off:], bp, m - 256, n, k)
+    assert torch.equal(part, want[256:])
     tcec.device_status()
+
+
+@pytest.mark.parametrize("policy", ["fp16_ec", "fp16_no_ec", "tf32_ec"])
+def test_packed_sub_ranges_stay_inside_exactly_sized_buffers(policy):
+    """Sub-ranges of packed A and B (the 256-wide tiles and the CTA-pair kernel read row blocks in
+    pairs) placed at the very end of a buffer: nothing beyond the operand may be read, and the
+    result equals the matching rows and columns of the full product."""
+    rng = np.random.default_rng(43)
+    m, n, k = 768, 1024, 160
+    a = _t(rng.standard_normal((m, k)).astype(np.float32))
+    b = _t(rng.standard_normal((k, n)).astype(np.float32))
+    want = tcec.sgemm(a, b, policy=policy)
+    na, nb = tcec.packed_bytes(m, k, policy), tcec.packed_bytes(n, k, policy)
+    # one arena: [A packed][B packed]; the last sub-range of each ends exactly at its operand's end
+    arena = torch.full((na + nb,), 0xFF, dtype=torch.uint8, device=DEV)  # 0xFFFF = a NaN in fp16, 0xFFFFFFFF in tf32
+    tcec.pack_a(a, policy, out=arena[:na])
+    tcec.pack_b(b, policy, out=arena[na:])
+    oa, ob = tcec.packed_row_offset(512, k, policy), tcec.packed_row_offset(768, k, policy)
+    assert oa and ob and na - oa == tcec.packed_bytes(256, k, policy) and nb - ob == tcec.packed_bytes(256, k, policy)
+    # A's last 256 rows: the sub-range ends where B's NaN-free data begins, so an over-read would change nothing
+    # visible; therefore use a second arena whose tail is NaN for the check of A
+    tail = torch.full((na + 4096,), 0xFF, dtype=torch.uint8, device=DEV)
+    tail[:na] = arena[:na]
+    got_a = tcec.sgemm_packed(tail[oa:], arena[na:], 256, n, k, policy=policy)
+    got_b = tcec.sgemm_packed(arena[:na], torch.cat([arena[na:], torch.full((4096,), 0xFF, dtype=torch.uint8, device=DEV)])[ob:],
+                              m, 256, k, policy=policy)
+    tcec.device_status()
+    assert torch.equal(got_a, want[512:])
+    assert torch.equal(got_b, want[:, 768:])
 
 
 # ---------------------------------------------------------------- cuBLAS-convention entry points
@@ -501,11 +530,13 @@ def test_cublas_convention_calls():
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref was not built")
 @pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec"])
 @pytest.mark.parametrize("dist_name", ["uniform", "normal", "positive"])
-def test_error_no_worse_than_twice_the_reference(policy, dist_name):
+@pytest.mark.parametrize("k", [4096, 16384, 32768])
+def test_error_no_worse_than_twice_the_reference(policy, dist_name, k):
     """Acceptance bound: max relative error vs FP64 <= 2x the reference TCEC kernel's and
-    <= 2x an FP32 SGEMM's, on identical inputs."""
+    <= 2x an FP32 SGEMM's, on identical inputs.  K = 16384 and 32768 are where the automatic
+    promotion interval is longest (512), i.e. where the margin is thinnest."""
     torch.manual_seed(50)
-    m, n, k = 1024, 768, 4096
+    m, n = (1024, 768) if k == 4096 else (1024, 1024)
     if dist_name == "uniform":
         a, b = torch.rand(m, k, device=DEV) * 2 - 1, torch.rand(k, n, device=DEV) * 2 - 1
     elif dist_name == "normal":
@@ -585,8 +616,9 @@ def test_batched_configuration_full_size_properties():
     c2 = [torch.empty((n, n), device=DEV) for _ in range(64)]
     tcec.sgemm_batched(list(a[:64]), list(b[:64]), c2)
     tcec.device_status()
-    # (the pointer-array form goes through the panel kernel: same products, same rounding points)
-    assert all(torch.allclose(x, y, rtol=0, atol=2e-5) for x, y in zip(c2, c[:64]))
+    # the pointer-array form goes through the panel kernel, the strided form through the FP32-tile
+    # kernel: same split, same products, same rounding points, so not a bit differs
+    assert all(torch.equal(x, y) for x, y in zip(c2, c[:64]))
 
 
 def test_column_block_configuration_full_size_properties():
@@ -630,7 +662,11 @@ def test_column_sharded_driver_on_one_gpu(tmp_path):
         a = torch.randn((m, k), generator=g, device=DEV)
         b = torch.randn((k, n), generator=g, device=DEV)
         c = torch.full((m, n), float("nan"), device=DEV)
-        sharded.sgemm_column_sharded(a, b, c, m, k, root=0, panel_rows=256)
+        tcec.set_option("comm_panel_rows", 256)  # several panels at this size
+        try:
+            sharded.sgemm_column_sharded(a, b, c, m, k, root=0)
+        finally:
+            tcec.set_option("comm_panel_rows", 2048)
         tcec.device_status()
         assert torch.equal(c, tcec.sgemm(a, b))
         first, count = sharded.batch_shard(10, 0, 1)
@@ -639,3 +675,44 @@ def test_column_sharded_driver_on_one_gpu(tmp_path):
                            tcec.sgemm_strided_batched(ab, bb))
     finally:
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------- host operands
+@pytest.mark.parametrize("la,lb,lc", [("row", "row", "row"), ("col", "row", "col"), ("row", "col", "row")])
+def test_host_operand_gemm_matches_device_call(la, lb, lc):
+    """tcec_sgemm_host (copy-in, GEMM and copy-out pipelined in row panels) gives the bits of
+    tcec_sgemm on the same operands, for every layout, with alpha and beta, padded leading
+    dimensions, and a result that is complete once the stream is."""
+    rng = np.random.default_rng(70)
+    m, n, k = 900, 520, 300
+
+    def host(x, layout, pad):
+        r, c = x.shape
+        if layout == "row":
+            buf = torch.full((r, c + pad), float("nan")).pin_memory()
+            v = buf[:, :c]
+        else:
+            buf = torch.full((c, r + pad), float("nan")).pin_memory()
+            v = buf[:, :r].t()
+        v.copy_(torch.from_numpy(x))
+        return buf, v
+
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    c0 = rng.standard_normal((m, n)).astype(np.float32)
+    _, ah = host(a, la, 4)
+    _, bh = host(b, lb, 0)
+    for alpha, beta in ((1.0, 0.0), (1.5, -0.5)):
+        cbuf, ch = host(c0, lc, 3)
+        tcec.sgemm_host(ah, bh, ch, alpha=alpha, beta=beta, panel_rows=256)
+        torch.cuda.current_stream().synchronize()
+        tcec.device_status()
+        cd = _t(c0).clone() if lc == "row" else _t(c0.T).clone().t()
+        want = tcec.sgemm(_t(a), _t(b), cd, alpha=alpha, beta=beta)
+        assert torch.equal(ch, want.cpu()), (la, lb, lc, alpha)
+        assert torch.isnan(cbuf).sum() == cbuf.numel() - m * n  # the padding of C is untouched
+    # k == 0 scales C only
+    cbuf, ch = host(c0, lc, 0)
+    tcec.sgemm_host(ah[:, :0], bh[:0, :], ch, beta=2.0)
+    torch.cuda.current_stream().synchronize()
+    assert torch.equal(ch, torch.from_numpy(2 * c0))

@@ -52,6 +52,32 @@ def test_static_entry_matches_the_allocating_one_twice_in_a_row():
         assert torch.equal(got, want)  # same kernels on the same panels: not a bit differs
 
 
+def test_static_entry_allocates_nothing():
+    """The property the entry point exists for: after its one-time set-up, a call leaves the
+    device's free memory exactly as it found it - also for a shape that makes the allocating
+    entry point take a new workspace from the device."""
+    tcec.destroy()  # drop every cached workspace, so that tcec_sgemm has to allocate again below
+    a1, b1, c1 = torch.rand((1024, 512), device=DEV), torch.rand((512, 768), device=DEV), torch.empty((1024, 768), device=DEV)
+    a2, b2, c2 = torch.rand((2048, 256), device=DEV), torch.rand((256, 1536), device=DEV), torch.empty((2048, 1536), device=DEV)
+    want = torch.empty((2048, 1536), device=DEV)
+    tcec.sgemm_static(a1, b1, c1)  # first call on the device: looks up the array's address, sets kernel attributes
+    tcec.static_status()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    tcec.sgemm_static(a2, b2, c2)  # a larger problem than any before it
+    tcec.sgemm_static(a1, b1, c1)
+    tcec.static_status()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "tcec_sgemm_static changed the device's free memory"
+    # the allocating entry point, by contrast, takes its workspace from the device here
+    tcec.sgemm(a2, b2, want)
+    torch.cuda.synchronize()
+    free_alloc, _ = torch.cuda.mem_get_info()
+    assert free_alloc <= free_after - tcec.workspace_bytes(2048, 1536, 256) // 2
+    assert torch.equal(c2, want)
+
+
 def test_static_entry_rejects_what_does_not_fit_and_bad_arguments():
     lib = tcec.load()
     limit = lib.tcec_static_scratch_bytes()

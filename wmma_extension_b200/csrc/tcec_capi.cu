@@ -9,51 +9,27 @@
 #include <mutex>
 #include <utility>
 
-#include "../../include/tcec.h"
 #include "tcec_gemm_fused.cuh"
 #include "tcec_gemm_panels.cuh"
 #include "tcec_gemm_panels_pair.cuh"
+#include "tcec_internal.h"
 #include "tcec_panels.cuh"
 
 using namespace tcec_sm100;
 
+namespace tcec_host {
+
 namespace {
-
-struct Workspace {
-  void* ptr = nullptr;
-  size_t bytes = 0;
-};
-struct DeviceState {
-  int* status = nullptr;
-  int sm_count = 0;
-  bool attrs_done = false;
-  std::map<cudaStream_t, Workspace> ws;
-  std::map<cudaStream_t, unsigned int*> sched;  // per stream: the panel GEMM's two tile-scheduler counters
-  unsigned int* sched_fixed = nullptr;          // set instead by the allocation-free entry (a device symbol)
-};
-
 std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
-int g_promote_k = -1;  // -1: chosen per call from K and the policy
-int g_tile_n = 0;
-int g_store_turn = 1;  // 0: the panel kernel stores directly and leaves ~30 KB of shared memory per SM free
-int g_static_tiles = 0;  // 0: tiles beyond the first wave are drawn from a device-wide counter; 1: static striding
-int g_reserve_sms = 0;  // SMs the panel GEMM leaves idle (for a caller's communication kernels)
-int g_cta_pair = -1;  // -1: CTA-pair kernel for the policies without error correction; 0: never; 1: whenever it applies
-int g_path = 0;  // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
-#ifdef TCEC_DEVELOP
-int g_debug_flags = 0;               // switches that leave out parts of a kernel (results invalid)
-unsigned long long* g_trace = nullptr;  // device buffer for hand-off timestamps
-#else
-constexpr int g_debug_flags = 0;
-constexpr unsigned long long* g_trace = nullptr;
-#endif
+Options g_opt;
+}  // namespace
 
-#define TCEC_CUDA(call)                        \
-  do {                                         \
-    cudaError_t e_ = (call);                   \
-    if (e_ != cudaSuccess) return TCEC_ERR_CUDA; \
-  } while (0)
+std::mutex& state_mutex() { return g_mu; }
+Options snapshot_options() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  return g_opt;
+}
 
 template <int BN, bool T, bool E>
 cudaError_t set_smem_attr() {
@@ -99,16 +75,15 @@ int get_device_state(DeviceState** out) {
   return TCEC_OK;
 }
 
-int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out) {
+// A workspace that must grow is replaced; the old buffer is handed back in *to_free so that the
+// caller can wait for the stream and free it after it has released the state mutex.
+int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out, void** to_free) {
   Workspace& w = st->ws[stream];
+  *to_free = nullptr;
   if (w.bytes < bytes) {
-    if (w.ptr) {
-      // Work queued on this stream may still read the old buffer.
-      TCEC_CUDA(cudaStreamSynchronize(stream));
-      cudaFree(w.ptr);
-      w.ptr = nullptr;
-      w.bytes = 0;
-    }
+    *to_free = w.ptr;
+    w.ptr = nullptr;
+    w.bytes = 0;
     if (cudaMalloc(&w.ptr, bytes) != cudaSuccess) {
       w.ptr = nullptr;
       return TCEC_ERR_ALLOC;
@@ -117,6 +92,13 @@ int get_workspace(DeviceState* st, cudaStream_t stream, size_t bytes, void** out
   }
   *out = w.ptr;
   return TCEC_OK;
+}
+// Work queued on the stream may still read a replaced workspace: wait for it, then free.
+static int release_old_workspace(void* old, cudaStream_t stream) {
+  if (!old) return TCEC_OK;
+  const cudaError_t e = cudaStreamSynchronize(stream);
+  cudaFree(old);
+  return e == cudaSuccess ? TCEC_OK : TCEC_ERR_CUDA;
 }
 
 // Launches on one stream are ordered, so they can share one pair of counters (each launch leaves
@@ -138,11 +120,6 @@ int get_sched(DeviceState* st, cudaStream_t stream, unsigned int** out) {
   return TCEC_OK;
 }
 
-struct Shape {
-  int tile_n, tiles_m, tiles_n, nkb, kop, np;
-  int a_row_blocks, b_row_blocks;  // 128-row panel blocks, padded to an even count
-  size_t a_bytes, b_bytes;         // per matrix
-};
 bool policy_tf32(int policy) { return policy == TCEC_POLICY_TF32_EC || policy == TCEC_POLICY_TF32_NO_EC; }
 bool policy_ec(int policy) { return policy == TCEC_POLICY_FP16_EC || policy == TCEC_POLICY_TF32_EC; }
 int padded_row_blocks(int rows) { return ((rows + 255) / 256) * 2; }
@@ -158,16 +135,16 @@ size_t packed_bytes(int rows, int k, int policy) {
 // all-positive inputs included, where the truncation bias is largest); the
 // policies without error correction keep the reference's default for them, accumulation inside
 // the tensor core (mma_rz_sync, include/wmma_extension/tcec/detail/no_cor.hpp:858-897).
-int promote_blocks(int k, int policy, int kop) {
-  int pk = g_promote_k;
+int promote_blocks(int k, int policy, int kop, const Options& opt) {
+  int pk = opt.promote_k;
   if (pk < 0) pk = !policy_ec(policy) ? 0 : (k <= 2048 ? 64 : (k <= 4096 ? 128 : (k < 16384 ? 256 : 512)));
   return pk > 0 ? (pk + kop - 1) / kop : 0;
 }
-Shape plan(int m, int n, int k, int policy) {
+Shape plan(int m, int n, int k, int policy, const Options& opt) {
   Shape s;
   s.kop = policy_tf32(policy) ? 16 : 32;
   s.np = policy_ec(policy) ? 2 : 1;
-  s.tile_n = g_tile_n ? g_tile_n : (n > 128 ? 256 : 128);
+  s.tile_n = opt.tile_n ? opt.tile_n : (n > 128 ? 256 : 128);
   s.tiles_m = (m + 127) / 128;
   s.tiles_n = (n + s.tile_n - 1) / s.tile_n;
   s.nkb = (k + s.kop - 1) / s.kop;
@@ -215,29 +192,17 @@ void launch_split(const SplitParams& sp, int batch, cudaStream_t stream) {
 }
 
 template <int BN, bool T, bool E>
-void launch_gemm(const GemmPanelParams& gp, int sm_count, cudaStream_t stream) {
+void launch_gemm(const GemmPanelParams& gp, int grid, cudaStream_t stream) {
   using Cfg = GemmPanelCfg<BN, T, E>;
-  const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * gp.batch;
-  const int sms = sm_count - g_reserve_sms > 1 ? sm_count - g_reserve_sms : 1;
-  const int grid = static_cast<int>(ntiles < sms ? ntiles : sms);
   tcec_gemm_panels_kernel<BN, T, E>
       <<<grid, Cfg::THREADS, gp.store_turn ? Cfg::SMEM_BYTES : Cfg::SMEM_BYTES_NO_TURN, stream>>>(gp);
 }
 
 bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
 
-// Split one operand (A: rows = m; B: rows = n) into panels on `stream`.
-// `part` describes an operand that is one half of a K-concatenated panel set built from
-// interleaved complex data: element stride 2, a sign, and where its k blocks go.
-struct PackPart {
-  int elem_stride = 1;
-  float mul = 1.0f;
-  int kb_offset = 0;
-  int nkb_out = 0;
-};
 void pack_operand(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
                   long long ld, long long stride, int batch, uint8_t* panels, size_t panels_stride,
-                  int policy, cudaStream_t stream, const PackPart& part = PackPart()) {
+                  int policy, cudaStream_t stream, const PackPart& part) {
   const int kop = policy_tf32(policy) ? 16 : 32;
   SplitParams sp{};
   sp.src = src;
@@ -264,10 +229,12 @@ void pack_operand(bool k_contiguous, int rows, int k, const float* src, const fl
   }
 }
 
-int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t* panels_a,
-                 size_t a_stride, const uint8_t* panels_b, size_t b_stride, float beta, float* c,
-                 float* const* c_array, long long ldc, long long stride_c, int lc, int batch,
-                 int policy, DeviceState* st, cudaStream_t stream) {
+int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t* panels_a, size_t a_stride,
+                const uint8_t* panels_b, size_t b_stride, float beta, float* c, float* const* c_array, long long ldc,
+                long long stride_c, int lc, int batch, int policy, DeviceState* st, cudaStream_t stream,
+                const Options& opt, const LaunchExtras* extras) {
+  const LaunchExtras none;
+  const LaunchExtras& ex = extras ? *extras : none;
   GemmPanelParams gp{};
   gp.M = m;
   gp.N = n;
@@ -276,7 +243,7 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
   gp.nkb = s.nkb;
   gp.tiles_m = s.tiles_m;
   gp.tiles_n = s.tiles_n;
-  gp.promo = promote_blocks(k, policy, s.kop);
+  gp.promo = promote_blocks(k, policy, s.kop, opt);
   gp.alpha = alpha;
   gp.beta = beta;
   gp.panels_a = panels_a;
@@ -289,22 +256,24 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
   gp.c_batch_stride = stride_c;
   gp.c_col_major = (lc == TCEC_COL_MAJOR);
   gp.status = st->status;
-  gp.debug_flags = g_debug_flags;
-  gp.store_turn = g_store_turn;
-  if (!g_static_tiles) {
-    const int rc = get_sched(st, stream, &gp.sched);
-    if (rc != TCEC_OK) return rc;
-  }
-  gp.trace = g_trace;
+  gp.debug_flags = opt.debug_flags;
+  gp.store_turn = opt.store_turn;
+  gp.trace = opt.trace;
+  gp.row_ready = ex.row_ready;
+  gp.ready_rows = ex.ready_rows;
+  gp.ready_epoch = ex.ready_epoch;
+  const int reserve = ex.reserve_sms >= 0 ? ex.reserve_sms : opt.reserve_sms;
+  const int sms = st->sm_count - reserve > 1 ? st->sm_count - reserve : 1;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
   // One product per K block makes the kernel wait on operands from L2, which a CTA pair halves
   // for B: measured 10-15 % faster there, and no faster (slower at the power cap) with three products.
-  const bool want_pair = g_cta_pair == 1 || (g_cta_pair == -1 && !ec);
+  const bool want_pair = !ex.force_one_sm && !ex.row_ready && !ex.sched &&
+                         (opt.cta_pair == 1 || (opt.cta_pair == -1 && !ec));
   if (want_pair && s.tile_n == 256 && m > 128) {
-    // CTA pairs: 256 x 256 tiles, grid of up to sm_count/2 clusters of two CTAs
+    // CTA pairs: 256 x 256 tiles, grid of up to sms/2 clusters of two CTAs
     gp.tiles_m = (m + 255) / 256;
     const long long npair_tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
-    const int max_pairs = st->sm_count / 2;
+    const int max_pairs = sms / 2 > 1 ? sms / 2 : 1;
     const int grid = 2 * static_cast<int>(npair_tiles < max_pairs ? npair_tiles : max_pairs);
     if (tf32 && ec)
       tcec_gemm_panels_pair_kernel<true, true><<<grid, 384, GemmPairCfg<true, true>::SMEM_BYTES, stream>>>(gp);
@@ -316,12 +285,28 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
       tcec_gemm_panels_pair_kernel<false, false><<<grid, 384, GemmPairCfg<false, false>::SMEM_BYTES, stream>>>(gp);
     return TCEC_OK;
   }
-#define TCEC_DISPATCH(T, E)                                      \
-  do {                                                           \
-    if (s.tile_n == 256)                                         \
-      launch_gemm<256, T, E>(gp, st->sm_count, stream);          \
-    else                                                         \
-      launch_gemm<128, T, E>(gp, st->sm_count, stream);          \
+  const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
+  int grid = static_cast<int>(ntiles < sms ? ntiles : sms);
+  if (ex.sched) {
+    // counters shared with other launches of the same problem; the caller zeroes them
+    gp.sched = ex.sched;
+    gp.sched_keep = 1;
+    gp.sched_base = ex.sched_base;
+    gp.sched_all_dynamic = ex.all_from_counter;
+    if (ex.grid > 0) grid = ex.grid;
+  } else {
+    if (!opt.static_tiles) {
+      const int rc = get_sched(st, stream, &gp.sched);
+      if (rc != TCEC_OK) return rc;
+    }
+    gp.sched_base = grid;
+  }
+#define TCEC_DISPATCH(T, E)                         \
+  do {                                              \
+    if (s.tile_n == 256)                            \
+      launch_gemm<256, T, E>(gp, grid, stream);     \
+    else                                            \
+      launch_gemm<128, T, E>(gp, grid, stream);     \
   } while (0)
   if (tf32 && ec)
     TCEC_DISPATCH(true, true);
@@ -387,10 +372,10 @@ bool tma_addressable(const float* base, long long ld, long long stride, int batc
 bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const float* a, long long lda,
                long long stride_a, const float* b, long long ldb, long long stride_b, float beta, float* c,
                long long ldc, long long stride_c, int batch, int policy, const DeviceState* st,
-               cudaStream_t stream) {
+               cudaStream_t stream, const Options& opt) {
   if (policy_tf32(policy) || !a || !b || !c || n <= 128) return false;
   // Worth it only where the GEMM is bound by DRAM traffic, which the split pass doubles: short K.
-  const bool wanted = g_path == 2 || (g_path == 0 && batch > 1 && k <= 512);
+  const bool wanted = opt.path == 2 || (opt.path == 0 && batch > 1 && k <= 512);
   if (!wanted) return false;
   if (!tma_addressable(a, lda, stride_a, batch) || !tma_addressable(b, ldb, stride_b, batch)) return false;
   const bool a_kc = (la == TCEC_ROW_MAJOR), b_kc = (lb == TCEC_COL_MAJOR);
@@ -410,7 +395,7 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   fp.nkb = (k + 31) / 32;
   fp.tiles_m = (m + 255) / 256;  // 256 x 256 tiles on CTA pairs
   fp.tiles_n = (n + 255) / 256;
-  fp.promo = promote_blocks(k, policy, 32);
+  fp.promo = promote_blocks(k, policy, 32, opt);
   fp.a_k_contiguous = a_kc;
   fp.b_k_contiguous = b_kc;
   fp.alpha = alpha;
@@ -420,10 +405,11 @@ bool try_fused(int la, int lb, int lc, int m, int n, int k, float alpha, const f
   fp.c_batch_stride = stride_c;
   fp.c_col_major = (lc == TCEC_COL_MAJOR);
   fp.status = st->status;
-  fp.debug_flags = g_debug_flags;
-  fp.trace = g_trace;
+  fp.debug_flags = opt.debug_flags;
+  fp.trace = opt.trace;
   const long long ntiles = static_cast<long long>(fp.tiles_m) * fp.tiles_n * batch;
-  const int max_pairs = st->sm_count / 2;
+  const int sms = st->sm_count - opt.reserve_sms > 2 ? st->sm_count - opt.reserve_sms : 2;
+  const int max_pairs = sms / 2;
   const int grid = 2 * static_cast<int>(ntiles < max_pairs ? ntiles : max_pairs);
   if (policy_ec(policy))
     tcec_gemm_fused_kernel<true><<<grid, GemmFusedCfg<true>::THREADS, GemmFusedCfg<true>::SMEM_BYTES, stream>>>(fp, map_a, map_b, map_c);
@@ -461,30 +447,45 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
   if (batch > 65535) return TCEC_ERR_UNSUPPORTED;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-  std::lock_guard<std::mutex> lock(g_mu);
+  // State is looked up (and a workspace grown) under the mutex; the launches run without it.
+  Options opt;
   DeviceState* st = nullptr;
-  int rc = get_device_state(&st);
-  if (rc != TCEC_OK) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    opt = g_opt;
+    const int rc = get_device_state(&st);
+    if (rc != TCEC_OK) return rc;
+  }
   if (k == 0 || alpha == 0.f) return scale_only(beta, c, c_array, ldc, stride_c, m, n, lc, batch, stream);
 
   if (!a_array && !b_array && !c_array &&
       try_fused(la, lb, lc, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc, stride_c, batch, policy,
-                st, stream)) {
+                st, stream, opt)) {
     TCEC_CUDA(cudaGetLastError());
     return TCEC_OK;
   }
-  const Shape s = plan(m, n, k, policy);
+  const Shape s = plan(m, n, k, policy, opt);
   void* ws = nullptr;
-  rc = get_workspace(st, stream, (s.a_bytes + s.b_bytes) * batch, &ws);
+  void* old = nullptr;
+  int rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    rc = get_workspace(st, stream, (s.a_bytes + s.b_bytes) * batch, &ws, &old);
+  }
+  const int rel = release_old_workspace(old, stream);
   if (rc != TCEC_OK) return rc;
+  if (rel != TCEC_OK) return rel;
   uint8_t* panels_a = static_cast<uint8_t*>(ws);
   uint8_t* panels_b = panels_a + s.a_bytes * batch;
   pack_operand(la == TCEC_ROW_MAJOR, m, k, a, a_array, lda, stride_a, batch, panels_a, s.a_bytes, policy,
                stream);
   pack_operand(lb == TCEC_COL_MAJOR, n, k, b, b_array, ldb, stride_b, batch, panels_b, s.b_bytes, policy,
                stream);
-  rc = gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
-                   lc, batch, policy, st, stream);
+  {
+    std::lock_guard<std::mutex> lock(g_mu);  // the per-stream tile counters may be created here
+    rc = gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
+                     lc, batch, policy, st, stream, opt);
+  }
   if (rc != TCEC_OK) return rc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
@@ -534,10 +535,15 @@ int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, 
     if (lda < (la == TCEC_ROW_MAJOR ? k : m) || ldb < (lb == TCEC_ROW_MAJOR ? n : k))
       return TCEC_ERR_INVALID_ARGUMENT;
   }
-  std::lock_guard<std::mutex> lock(g_mu);
+  Options opt;
   DeviceState* st = nullptr;
-  int rc = get_device_state(&st);
-  if (rc != TCEC_OK) return rc;
+  int rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    opt = g_opt;
+    rc = get_device_state(&st);
+    if (rc != TCEC_OK) return rc;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int inner = lc == TCEC_ROW_MAJOR ? n : m, outer = lc == TCEC_ROW_MAJOR ? m : n;
   const dim3 cgrid((inner + 255) / 256, outer < 32768 ? outer : 32768);
@@ -553,11 +559,17 @@ int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, 
   const long long k2_ll = 2ll * nkb * kop;
   if (k2_ll > 0x7fffffff) return TCEC_ERR_INVALID_ARGUMENT;
   const int k2 = static_cast<int>(k2_ll);
-  const Shape s = plan(m, n, k2, policy);
+  const Shape s = plan(m, n, k2, policy, opt);
   const size_t plane = ((static_cast<size_t>(m) * n * sizeof(float)) + 255) & ~static_cast<size_t>(255);
   void* ws = nullptr;
-  rc = get_workspace(st, stream, s.a_bytes + 2 * s.b_bytes + 2 * plane, &ws);
+  void* old = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    rc = get_workspace(st, stream, s.a_bytes + 2 * s.b_bytes + 2 * plane, &ws, &old);
+  }
+  const int rel = release_old_workspace(old, stream);
   if (rc != TCEC_OK) return rc;
+  if (rel != TCEC_OK) return rel;
   uint8_t* pa = static_cast<uint8_t*>(ws);
   uint8_t* pbr = pa + s.a_bytes;
   uint8_t* pbi = pbr + s.b_bytes;
@@ -578,9 +590,13 @@ int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, 
   pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbr, 0, policy, stream, neg);
   pack_operand(b_kc, n, k, b + 1, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, first);
   pack_operand(b_kc, n, k, b, nullptr, 2 * ldb, 0, 1, pbi, 0, policy, stream, second);
-  rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbr, 0, 0.0f, prod_r, nullptr, inner, 0, lc, 1, policy, st, stream);
-  if (rc != TCEC_OK) return rc;
-  rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbi, 0, 0.0f, prod_i, nullptr, inner, 0, lc, 1, policy, st, stream);
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbr, 0, 0.0f, prod_r, nullptr, inner, 0, lc, 1, policy, st, stream, opt);
+    if (rc == TCEC_OK)
+      rc = gemm_packed(s, m, n, k2, 1.0f, pa, 0, pbi, 0, 0.0f, prod_i, nullptr, inner, 0, lc, 1, policy, st, stream,
+                       opt);
+  }
   if (rc != TCEC_OK) return rc;
   cgemm_combine_kernel<<<cgrid, 256, 0, stream>>>(prod_r, prod_i, reinterpret_cast<float2*>(c), ldc, inner,
                                                   outer, al, be, 1);
@@ -588,7 +604,9 @@ int cgemm_impl(int la, int lb, int lc, int m, int n, int k, const float* alpha, 
   return TCEC_OK;
 }
 
-}  // namespace
+}  // namespace tcec_host
+
+using namespace tcec_host;
 
 extern "C" {
 
@@ -622,8 +640,9 @@ size_t tcec_packed_bytes(int rows, int k, int policy) {
 }
 
 size_t tcec_packed_row_offset(int row, int k, int policy) {
-  if (row < 0 || row % 128 != 0 || k <= 0 || policy < 0 || policy > 3) return 0;
-  return packed_bytes(256, k, policy) / 2 * static_cast<size_t>(row / 128);
+  // multiples of 256 only: the 256-wide tiles and the CTA-pair kernel read row blocks in pairs
+  if (row < 0 || row % 256 != 0 || k <= 0 || policy < 0 || policy > 3) return 0;
+  return packed_bytes(256, k, policy) * static_cast<size_t>(row / 256);
 }
 
 static int pack_entry(bool is_b, int layout, int rows, int k, const float* src, long long ld, void* packed,
@@ -635,10 +654,12 @@ static int pack_entry(bool is_b, int layout, int rows, int k, const float* src, 
   const bool k_contig = is_b ? (layout == TCEC_COL_MAJOR) : (layout == TCEC_ROW_MAJOR);
   if (ld < (k_contig ? k : rows)) return TCEC_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(packed) & 15) != 0) return TCEC_ERR_INVALID_ARGUMENT;
-  std::lock_guard<std::mutex> lock(g_mu);
-  DeviceState* st = nullptr;
-  const int rc = get_device_state(&st);
-  if (rc != TCEC_OK) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* st = nullptr;
+    const int rc = get_device_state(&st);
+    if (rc != TCEC_OK) return rc;
+  }
   pack_operand(k_contig, rows, k, src, nullptr, ld, 0, 1, static_cast<uint8_t*>(packed), 0, policy,
                static_cast<cudaStream_t>(stream));
   TCEC_CUDA(cudaGetLastError());
@@ -666,12 +687,13 @@ int tcec_sgemm_packed(int layout_c, int m, int n, int k, float alpha, const void
   DeviceState* st = nullptr;
   const int rc = get_device_state(&st);
   if (rc != TCEC_OK) return rc;
+  const Options opt = g_opt;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (k == 0 || alpha == 0.f) return scale_only(beta, c, nullptr, ldc, 0, m, n, layout_c, 1, s);
-  const Shape sh = plan(m, n, k, policy);
+  const Shape sh = plan(m, n, k, policy, opt);
   const int grc = gemm_packed(sh, m, n, k, alpha, static_cast<const uint8_t*>(a_packed), 0,
                               static_cast<const uint8_t*>(b_packed), 0, beta, c, nullptr, ldc, 0, layout_c, 1,
-                              policy, st, s);
+                              policy, st, s, opt);
   if (grc != TCEC_OK) return grc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
@@ -739,96 +761,59 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
 // hand-off timestamps.
 int tcec_debug_set_trace(unsigned long long* dev_buffer) {
   std::lock_guard<std::mutex> lock(g_mu);
-  g_trace = dev_buffer;
+  g_opt.trace = dev_buffer;
   return TCEC_OK;
 }
 #endif
 
+namespace {
+struct OptionEntry {
+  const char* name;
+  int Options::*field;
+  int lo, hi;
+  bool (*ok)(int);
+};
+bool any_value(int) { return true; }
+bool tile_value(int v) { return v == 0 || v == 128 || v == 256; }
+bool panel_rows_value(int v) { return v % 256 == 0; }
+const OptionEntry kOptions[] = {
+    {"promote_k", &Options::promote_k, -1, 0x7fffffff, any_value},
+    {"tile_n", &Options::tile_n, 0, 256, tile_value},
+    {"cta_pair", &Options::cta_pair, -1, 1, any_value},
+    {"path", &Options::path, 0, 2, any_value},
+    {"store_turn", &Options::store_turn, 0, 1, any_value},
+    {"reserve_sms", &Options::reserve_sms, 0, 64, any_value},
+    {"static_tiles", &Options::static_tiles, 0, 1, any_value},
+    {"comm_sms", &Options::comm_sms, 1, 64, any_value},
+    {"comm_panel_rows", &Options::comm_panel_rows, 256, 1 << 20, panel_rows_value},
+    {"comm_helper", &Options::comm_helper, 0, 1, any_value},
+#ifdef TCEC_DEVELOP
+    {"debug_flags", &Options::debug_flags, -0x7fffffff - 1, 0x7fffffff, any_value},
+#endif
+};
+const OptionEntry* find_option(const char* name) {
+  for (const OptionEntry& e : kOptions)
+    if (!strcmp(name, e.name)) return &e;
+  return nullptr;
+}
+}  // namespace
+
 int tcec_set_option(const char* name, int value) {
   if (!name) return TCEC_ERR_INVALID_ARGUMENT;
+  const OptionEntry* e = find_option(name);
+  if (!e || value < e->lo || value > e->hi || !e->ok(value)) return TCEC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(g_mu);
-  if (!strcmp(name, "promote_k")) {
-    if (value < -1) return TCEC_ERR_INVALID_ARGUMENT;
-    g_promote_k = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "tile_n")) {
-    if (value != 0 && value != 128 && value != 256) return TCEC_ERR_INVALID_ARGUMENT;
-    g_tile_n = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "cta_pair")) {
-    if (value < -1 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
-    g_cta_pair = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "path")) {
-    if (value < 0 || value > 2) return TCEC_ERR_INVALID_ARGUMENT;
-    g_path = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "store_turn")) {
-    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
-    g_store_turn = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "reserve_sms")) {
-    if (value < 0 || value > 64) return TCEC_ERR_INVALID_ARGUMENT;
-    g_reserve_sms = value;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "static_tiles")) {
-    if (value < 0 || value > 1) return TCEC_ERR_INVALID_ARGUMENT;
-    g_static_tiles = value;
-    return TCEC_OK;
-  }
-#ifdef TCEC_DEVELOP
-  if (!strcmp(name, "debug_flags")) {
-    g_debug_flags = value;
-    return TCEC_OK;
-  }
-#endif
-  return TCEC_ERR_INVALID_ARGUMENT;
+  g_opt.*(e->field) = value;
+  return TCEC_OK;
 }
 
 int tcec_get_option(const char* name, int* value) {
   if (!name || !value) return TCEC_ERR_INVALID_ARGUMENT;
+  const OptionEntry* e = find_option(name);
+  if (!e) return TCEC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(g_mu);
-  if (!strcmp(name, "promote_k")) {
-    *value = g_promote_k;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "tile_n")) {
-    *value = g_tile_n;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "cta_pair")) {
-    *value = g_cta_pair;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "path")) {
-    *value = g_path;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "store_turn")) {
-    *value = g_store_turn;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "reserve_sms")) {
-    *value = g_reserve_sms;
-    return TCEC_OK;
-  }
-  if (!strcmp(name, "static_tiles")) {
-    *value = g_static_tiles;
-    return TCEC_OK;
-  }
-#ifdef TCEC_DEVELOP
-  if (!strcmp(name, "debug_flags")) {
-    *value = g_debug_flags;
-    return TCEC_OK;
-  }
-#endif
-  return TCEC_ERR_INVALID_ARGUMENT;
+  *value = g_opt.*(e->field);
+  return TCEC_OK;
 }
 
 int tcec_device_status(int* detail) {
@@ -849,8 +834,7 @@ int tcec_device_status(int* detail) {
 
 size_t tcec_workspace_bytes(int m, int n, int k, int batch, int policy) {
   if (m <= 0 || n <= 0 || k <= 0 || batch <= 0 || policy < 0 || policy > 3) return 0;
-  std::lock_guard<std::mutex> lock(g_mu);
-  const Shape s = plan(m, n, k, policy);
+  const Shape s = plan(m, n, k, policy, snapshot_options());
   return (s.a_bytes + s.b_bytes) * batch;
 }
 
@@ -867,10 +851,12 @@ int tcec_destroy(void) {
     for (auto& sc : kv.second.sched)
       if (sc.second) cudaFree(sc.second);
     kv.second.sched.clear();
+    destroy_step_state(&kv.second);
     if (kv.second.status) cudaFree(kv.second.status);
     kv.second.status = nullptr;
     kv.second.attrs_done = false;
   }
+  destroy_comm_state();
   g_dev.clear();
   cudaSetDevice(cur);
   return TCEC_OK;
@@ -968,7 +954,8 @@ int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, in
     if (rc0 != TCEC_OK) return rc0;
     return scale_only(beta, c, nullptr, ldc, 0, m, n, layout_c, 1, stream);
   }
-  const Shape s = plan(m, n, k, policy);
+  const Options opt = g_opt;
+  const Shape s = plan(m, n, k, policy, opt);
   if (s.a_bytes + s.b_bytes > TCEC_STATIC_SCRATCH_BYTES) return TCEC_ERR_TOO_LARGE;
   StaticDevice* sd = nullptr;
   const int rc = static_device_state(&sd);
@@ -985,7 +972,7 @@ int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, in
   view.sm_count = sd->sm_count;
   view.sched_fixed = sd->sched;
   const int grc = gemm_packed(s, m, n, k, alpha, panels_a, 0, panels_b, 0, beta, c, nullptr, ldc, 0, layout_c, 1,
-                              policy, &view, stream);
+                              policy, &view, stream, opt);
   if (grc != TCEC_OK) return grc;
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
@@ -1017,6 +1004,7 @@ const char* tcec_status_string(int status) {
     case TCEC_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case TCEC_ERR_ALLOC: return "workspace allocation failed";
     case TCEC_ERR_TOO_LARGE: return "operands exceed the fixed scratch of the allocation-free entry point";
+    case TCEC_ERR_COMM: return "communication library (NCCL) missing, failed or not initialised";
     default: return "unknown status";
   }
 }

@@ -46,16 +46,24 @@ struct GemmPanelParams {
   long long ldc, c_batch_stride;
   int c_col_major;
   int* status;             // device word; non-zero after a wait ran out
-  unsigned int* sched;     // [0] tiles handed out beyond the first gridDim.x, [1] CTAs finished; both
+  unsigned int* sched;     // [0] tiles handed out beyond the first `sched_base`, [1] CTAs finished; both
                            // zero between launches (the last CTA to finish resets them); null = static
                            // striding (tile, tile + gridDim.x, ...)
+  int sched_base;          // tiles below this index are the first tiles of a launch's CTAs (CTA i takes tile i)
+  int sched_all_dynamic;   // 1: this launch's CTAs draw even their first tile from the counter (a second
+                           // launch that shares the counters of one already running)
+  int sched_keep;          // 1: the counters are shared by several launches and reset by the host
+  const unsigned int* row_ready;  // optional: one word per `ready_rows` rows of A; the producer loads a tile's
+  int ready_rows;                 // operands only once the word of the tile's rows equals `ready_epoch` (A is
+  unsigned int ready_epoch;       // arriving from another GPU while the kernel runs); the wait is bounded
   int store_turn;          // 1: stores go through the per-warp shared-memory buffers (launched with
                            // SMEM_BYTES); 0: direct stores, launched with SMEM_BYTES_NO_TURN
-  int debug_flags;         // develop builds only (results invalid): bit 0 = no operand copies after the first ring fill, bit 1 = no MMAs
+  int debug_flags;         // develop builds only (results invalid): bit 0 = no operand copies after the first ring
+                           // fill, bit 1 = no MMAs, bit 5 = one stage is never filled (makes the bounded waits run out)
   unsigned long long* trace;  // develop builds only: CTA 0 writes clock64() at hand-off points
 };
 
-enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3 };
+enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrOperandWait = 4 };
 
 template <int BN, bool kTf32, bool kEc>
 struct GemmPanelCfg {
@@ -164,7 +172,36 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       // instead of delaying the launch.  Every tile (and the end mark) is published to the
       // CTA's other roles through the tile ring.
       uint32_t tq = 0, tph = 0;
-      for (int tile = blockIdx.x; ok;) {
+      int err = kErrProducerWait;
+      int ready_upto = -1;  // last row group of A seen to have arrived
+      int tile = (p.sched && p.sched_all_dynamic) ? p.sched_base + static_cast<int>(atomicAdd(&p.sched[0], 1u))
+                                                  : static_cast<int>(blockIdx.x);
+      for (; ok;) {
+        TileCoord tc{0, 0, 0};
+        if (tile < ntiles) {
+          tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+          if (p.row_ready) {
+            // A is still arriving: wait (bounded, sleeping between polls) for this tile's rows
+            const int grp = (tc.mt * 128) / p.ready_rows;
+            if (grp > ready_upto) {
+              bool seen = false;
+              for (uint32_t i = 0; i < TCEC_WAIT_LIMIT && !seen; ++i) {
+                if (ld_acquire_gpu(p.row_ready + grp) == p.ready_epoch) seen = true;
+                else {
+                  __nanosleep(256);
+                  if ((i & 0xff) == 0xff && *abortp) break;
+                }
+              }
+              if (!seen) {
+                ok = false;
+                err = kErrOperandWait;
+                break;
+              }
+              fence_proxy_async_global();  // the bulk copies below read what that flag announced
+              ready_upto = grp;
+            }
+          }
+        }
         if (!mbar_wait(smem_u32(&bar_tile_empty[tq]), tph ^ 1, abortp, 64)) {
           ok = false;
           break;
@@ -176,7 +213,6 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
           tph ^= 1;
         }
         if (tile >= ntiles) break;
-        const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
         // The next tile is claimed late in this one (two ring fills before its end), so the claim
         // follows the CTA's actual progress, and early enough for the atomic's latency to hide.
         int next_tile = tile + static_cast<int>(gridDim.x);
@@ -190,13 +226,15 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
             ok = false;
             break;
           }
-          if (p.sched && kb == claim_kb) next_tile = static_cast<int>(gridDim.x + atomicAdd(&p.sched[0], 1u));
+          if (p.sched && kb == claim_kb) next_tile = p.sched_base + static_cast<int>(atomicAdd(&p.sched[0], 1u));
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
           if (dev_flag(p.debug_flags, 1) && it >= static_cast<uint32_t>(NST)) {
             mbar_arrive(full);
             continue;
           }
+          // injected stall (failure-path test): the first stage after the first ring fill is never filled
+          if (dev_flag(p.debug_flags, 32) && it == static_cast<uint32_t>(NST)) continue;
           mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
@@ -214,7 +252,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
       }
       if (!ok) {
         abort_flag = 1;
-        atomicCAS(p.status, 0, kErrProducerWait);
+        atomicCAS(p.status, 0, err);
         // Let this thread's own copies land before the CTA gives up its shared memory.
         for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
           if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_full[q]), (armed_parity >> q) & 1);
@@ -324,7 +362,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base_s, Cfg::TMEM_COLS);
-  if (threadIdx.x == 0 && p.sched) {
+  if (threadIdx.x == 0 && p.sched && !p.sched_keep) {
     // Every CTA has drawn its last tile by now; the last one out leaves the counters at zero.
     __threadfence();
     if (atomicAdd(&p.sched[1], 1u) == gridDim.x - 1) {

@@ -1,4 +1,4 @@
-"""Multi-GPU execution of the TCEC SGEMM: one process per GPU over ``torch.distributed``.
+"""Multi-GPU execution of the TCEC SGEMM with one process per GPU over ``torch.distributed``.
 
 Two shardings, neither of which splits K, so no reduction is ever needed:
 
@@ -6,13 +6,16 @@ Two shardings, neither of which splits K, so no reduction is ever needed:
   batched GEMM; there is no collective on the data path.
 * column sharding - rank r owns a block of columns of B and of C; A lives on one
   rank and is broadcast (NCCL over NVLink on GPUs) in row panels into every rank's
-  own memory, each panel's GEMM overlapping the next panel's broadcast.  B is split
-  into operand panels once per call, not once per row panel.
+  own memory.
 
-The reference is single-GPU (no collective call site exists in it); this module is
-the host logic the multi-GPU configurations of the benchmark add around the C ABI.
-The local compute functions are injectable so the same plumbing runs under the
-``gloo`` backend on CPU tensors in tests.
+On GPUs both are thin callers of the C ABI (``tcec_sgemm_column_shard``,
+``tcec_sgemm_strided_batched``): the library owns its NCCL communicator, created here from an
+id that ``torch.distributed`` carries to the ranks.  The same plumbing also runs with injected
+local compute under the ``gloo`` backend on CPU tensors, which is how its host logic - shard
+arithmetic, panel order, what happens when a rank fails - is tested without a GPU.
+
+The reference is single-GPU (no collective call site exists in it); this module is the host
+logic the multi-GPU configurations of the benchmark add around the C ABI.
 """
 from __future__ import annotations
 
@@ -21,6 +24,16 @@ from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+OK, ERR_LOCAL, ERR_COMM, ERR_PEER = 0, 1, 2, 3
+
+
+class ShardError(RuntimeError):
+    """A rank's local compute failed, a collective failed, or another rank reported a failure."""
+
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(what)
 
 
 def batch_shard(batch: int, rank: int, world: int) -> Tuple[int, int]:
@@ -57,83 +70,91 @@ def row_panels(m: int, panel_rows: int) -> List[Tuple[int, int]]:
 
 @dataclass
 class LocalOps:
-    """Local compute used by the sharded drivers (CUDA library by default)."""
+    """Local compute injected into the column-sharded driver (tests; a caller's own kernels)."""
 
     prepare_b: Callable[[torch.Tensor], object]
     gemm_panel: Callable[[torch.Tensor, object, torch.Tensor], None]  # (A panel, prepared B, C rows)
 
 
-def cuda_ops(policy: str = "fp16_ec", reserve_sms: int = 0) -> LocalOps:
-    """Local compute through the CUDA library.  The GEMM's persistent CTAs take every register
-    of their SM, so a broadcast kernel launched beside it only runs where the GEMM has no CTA,
-    and a GEMM CTA that has to wait for such an SM delays the whole launch.  ``reserve_sms`` keeps
-    that many SMs out of the GEMM's grid (as many as the broadcast uses channels)."""
+_comm_ready = {}
+
+
+def init_library_comm(group=None) -> None:
+    """Gives the CUDA library its own communicator for ``group`` (once): rank 0 obtains the id,
+    ``torch.distributed`` carries it, every rank joins with its current device."""
     from . import tcec
 
-    def prepare_b(b_local: torch.Tensor):
-        k, n = b_local.shape
-        return (tcec.pack_b(b_local, policy), k, n)
-
-    def gemm_panel(a_panel: torch.Tensor, prepared, c_rows: torch.Tensor) -> None:
-        b_packed, k, n = prepared
-        a_packed = tcec.pack_a(a_panel, policy)
-        if reserve_sms:
-            tcec.set_option("reserve_sms", reserve_sms)
-        try:
-            tcec.sgemm_packed(a_packed, b_packed, a_panel.shape[0], n, k, c_rows, policy=policy)
-        finally:
-            if reserve_sms:
-                tcec.set_option("reserve_sms", 0)
-
-    return LocalOps(prepare_b, gemm_panel)
+    key = id(group) if group is not None else 0
+    if _comm_ready.get(key):
+        return
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    box = [tcec.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    tcec.comm_init_rank(world, rank, box[0])
+    _comm_ready[key] = True
 
 
 def sgemm_column_sharded(a_root: Optional[torch.Tensor], b_local: torch.Tensor, c_local: torch.Tensor,
                          m: int, k: int, *, root: int = 0, panel_rows: int = 2048,
-                         ops: Optional[LocalOps] = None, group=None,
-                         a_buffers: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """C[:, cols] = A @ B[:, cols] on every rank, with A (m x k, row-major) held by ``root``.
+                         ops: Optional[LocalOps] = None, group=None, policy: str = "fp16_ec") -> torch.Tensor:
+    """C[:, cols] = A @ B[:, cols] on every rank, with A (m x k) held by ``root``.
 
-    ``b_local`` is this rank's (k x n_local) column block, ``c_local`` its (m x n_local)
-    output block.  A reaches the other ranks by broadcast, one row panel at a time,
-    double-buffered: panel p+1 is in flight while panel p is multiplied.  Every rank
-    ends up having read A only from its own memory.
+    ``b_local`` is this rank's (k x n_local) column block, ``c_local`` its (m x n_local) output
+    block.  Without ``ops`` the operands are CUDA tensors and the call is ``tcec_sgemm_column_shard``
+    (the library broadcasts split row panels of A with NCCL and multiplies them as they arrive).
+    With ``ops`` the broadcast runs here, panel by panel through ``torch.distributed``, and the
+    local compute is the caller's; a failure of any rank's compute is reported on every rank.
     """
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
-    ops = ops or cuda_ops()
     if rank == root:
-        if a_root is None or tuple(a_root.shape) != (m, k) or not a_root.is_contiguous():
-            raise ValueError("root must pass a contiguous (m, k) matrix")
+        if a_root is None or tuple(a_root.shape) != (m, k):
+            raise ValueError("root must pass an (m, k) matrix")
+    if ops is None:
+        from . import tcec
+
+        if world > 1:
+            init_library_comm(group)
+        return tcec.sgemm_column_shard(a_root if rank == root else None, b_local, c_local, m, k, root=root,
+                                       policy=policy)
+
     panels = row_panels(m, panel_rows)
-    prepared = ops.prepare_b(b_local) if b_local.shape[1] > 0 else None
-    if world == 1:
-        for r0, rows in panels:
-            if prepared is not None:
-                ops.gemm_panel(a_root[r0:r0 + rows], prepared, c_local[r0:r0 + rows])
-        return c_local
-
-    max_rows = max(rows for _, rows in panels) if panels else 0
-    if a_buffers is None and rank != root:
-        a_buffers = [torch.empty((max_rows, k), dtype=b_local.dtype, device=b_local.device) for _ in range(2)]
-
-    def panel_tensor(i: int) -> torch.Tensor:
-        r0, rows = panels[i]
+    status, what = OK, ""
+    prepared = None
+    try:
+        prepared = ops.prepare_b(b_local) if b_local.shape[1] > 0 else None
+    except Exception as e:  # keep taking part in the broadcasts: the other ranks must not block on this one
+        status, what = ERR_LOCAL, f"prepare_b failed on rank {rank}: {e}"
+    src = dist.get_global_rank(group, root) if group is not None else root
+    buf = None
+    for r0, rows in panels:
         if rank == root:
-            return a_root[r0:r0 + rows]
-        return a_buffers[i % 2][:rows]
-
-    works = [None] * len(panels)
-    if panels:
-        works[0] = dist.broadcast(panel_tensor(0), src=root, group=group, async_op=True)
-    for i, (r0, rows) in enumerate(panels):
-        works[i].wait()
-        if i + 1 < len(panels):
-            # Buffer (i+1) % 2 was last read by panel i-1's GEMM, queued on this stream before
-            # the wait above; the collective's stream is ordered after it by the work handle.
-            works[i + 1] = dist.broadcast(panel_tensor(i + 1), src=root, group=group, async_op=True)
-        if prepared is not None:
-            ops.gemm_panel(panel_tensor(i), prepared, c_local[r0:r0 + rows])
+            panel = a_root[r0:r0 + rows].contiguous()
+        else:
+            if buf is None or buf.shape[0] < rows:
+                buf = torch.empty((rows, k), dtype=b_local.dtype, device=b_local.device)
+            panel = buf[:rows]
+        if world > 1:
+            try:
+                dist.broadcast(panel, src=src, group=group)
+            except Exception as e:
+                raise ShardError(ERR_COMM, f"broadcast of rows {r0}..{r0 + rows} failed on rank {rank}: {e}") from e
+        if status == OK and prepared is not None:
+            try:
+                ops.gemm_panel(panel, prepared, c_local[r0:r0 + rows])
+            except Exception as e:
+                status, what = ERR_LOCAL, f"gemm_panel failed on rank {rank} at row {r0}: {e}"
+    if world > 1:
+        # every rank learns whether any rank failed (the only extra collective: one word per call)
+        word = torch.tensor([status], dtype=torch.int32, device=b_local.device)
+        try:
+            dist.all_reduce(word, op=dist.ReduceOp.MAX, group=group)
+        except Exception as e:
+            raise ShardError(ERR_COMM, f"status exchange failed on rank {rank}: {e}") from e
+        if status == OK and int(word.item()) != OK:
+            status, what = ERR_PEER, "another rank reported a failure"
+    if status != OK:
+        raise ShardError(status, what)
     return c_local
 
 

@@ -21,7 +21,8 @@ LIB_PATH = os.path.join(_HERE, "libtcec_b200.so")
 
 ROW_MAJOR, COL_MAJOR = 0, 1
 POLICIES = {"fp16_ec": 0, "tf32_ec": 1, "fp16_no_ec": 2, "tf32_no_ec": 3}
-OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_ALLOC, ERR_TOO_LARGE = range(7)
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_ALLOC, ERR_TOO_LARGE, ERR_COMM = range(8)
+COMM_ID_BYTES = 128
 
 EXPORTED_SYMBOLS = (
     "tcec_sgemm",
@@ -36,6 +37,15 @@ EXPORTED_SYMBOLS = (
     "tcec_cgemm",
     "tcec_sgemm_cublas",
     "tcec_sgemm_batched_cublas",
+    "tcec_sgemm_host",
+    "tcec_sgemm_multi",
+    "tcec_sgemm_batched_multi",
+    "tcec_comm_set_library",
+    "tcec_comm_unique_id",
+    "tcec_comm_init_rank",
+    "tcec_comm_destroy",
+    "tcec_sgemm_column_shard",
+    "tcec_sgemm_column_shard_host",
     "tcec_sgemm_static",
     "tcec_static_scratch_bytes",
     "tcec_static_status",
@@ -96,6 +106,25 @@ def load() -> ctypes.CDLL:
     lib.tcec_static_scratch_bytes.restype = sz
     lib.tcec_static_status.argtypes = [ctypes.POINTER(i)]
     lib.tcec_static_status.restype = i
+    lib.tcec_sgemm_host.argtypes = [i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, i, p]
+    lib.tcec_sgemm_host.restype = i
+    ip, pp, llp = ctypes.POINTER(i), ctypes.POINTER(p), ctypes.POINTER(ll)
+    lib.tcec_sgemm_multi.argtypes = [i, ip, i, i, i, i, ip, i, f, p, ll, pp, llp, f, pp, llp, i, pp]
+    lib.tcec_sgemm_multi.restype = i
+    lib.tcec_sgemm_batched_multi.argtypes = [i, ip, i, i, i, i, i, i, f, pp, ll, ll, pp, ll, ll, f, pp, ll, ll, ip, i, pp]
+    lib.tcec_sgemm_batched_multi.restype = i
+    lib.tcec_comm_set_library.argtypes = [ctypes.c_char_p]
+    lib.tcec_comm_set_library.restype = i
+    lib.tcec_comm_unique_id.argtypes = [p]
+    lib.tcec_comm_unique_id.restype = i
+    lib.tcec_comm_init_rank.argtypes = [i, i, p]
+    lib.tcec_comm_init_rank.restype = i
+    lib.tcec_comm_destroy.argtypes = []
+    lib.tcec_comm_destroy.restype = i
+    lib.tcec_sgemm_column_shard.argtypes = [i, i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, p]
+    lib.tcec_sgemm_column_shard.restype = i
+    lib.tcec_sgemm_column_shard_host.argtypes = [i, i, i, i, i, i, i, f, p, ll, p, ll, f, p, ll, i, i, p]
+    lib.tcec_sgemm_column_shard_host.restype = i
     lib.tcec_cgemm.argtypes = [i, i, i, i, i, i, fp, p, ll, p, ll, fp, p, ll, i, p]
     lib.tcec_cgemm.restype = i
     lib.tcec_split.argtypes = [p, p, p, sz, i, p]
@@ -350,74 +379,141 @@ def sgemm_packed(a_packed: torch.Tensor, b_packed: torch.Tensor, m: int, n: int,
     return c
 
 
-_host_ctx = {}
+def _require_host_f32(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t.is_cuda or t.dtype != torch.float32:
+            raise ValueError("host operands must be float32 CPU tensors")
 
 
-def sgemm_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, *, policy="fp16_ec",
-               panel_rows: int = 2048, device: Optional[torch.device] = None) -> torch.Tensor:
-    """C = A @ B for operands in (pinned) HOST memory; the result is written to ``c_host``.
+def sgemm_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, *, alpha: float = 1.0,
+               beta: float = 0.0, policy="fp16_ec", panel_rows: int = 2048,
+               device: Optional[torch.device] = None) -> torch.Tensor:
+    """C = alpha * A @ B + beta * C for operands in (pinned) HOST memory, through ``tcec_sgemm_host``.
 
     B is copied and split once; A travels in row panels, so that the copy-in of panel p+1, the
-    GEMM on panel p and the copy-out of panel p-1 overlap on three streams (PCIe is full duplex).
-    Returns after the last copy-out has completed.  Device staging buffers are cached per shape.
+    GEMM on panel p and the copy-out of panel p-1 overlap on three streams.  The call returns
+    when everything is queued: ``c_host`` is complete once the current CUDA stream has reached
+    the end of the call's work (synchronise it before reading).
     """
-    for t in (a_host, b_host, c_host):
-        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
-            raise ValueError("host operands must be contiguous float32 CPU tensors")
+    _require_host_f32(a_host, b_host, c_host)
     m, k = a_host.shape
     k2, n = b_host.shape
     if k != k2 or tuple(c_host.shape) != (m, n):
         raise ValueError("shape mismatch")
+    la, lda = _layout_ld(a_host)
+    lb, ldb = _layout_ld(b_host)
+    lc, ldc = _layout_ld(c_host)
     dev = device or torch.device("cuda", torch.cuda.current_device())
-    panel_rows = max(128, (min(panel_rows, m) + 127) // 128 * 128)
-    key = (dev.index, m, n, k, panel_rows, _policy(policy))
-    ctx = _host_ctx.get(key)
-    if ctx is None:
-        _host_ctx.clear()  # one cached shape at a time
-        with torch.cuda.device(dev):
-            ctx = {
-                "s_in": torch.cuda.Stream(), "s_out": torch.cuda.Stream(),
-                "b": torch.empty((k, n), dtype=torch.float32, device=dev),
-                "bp": torch.empty(packed_bytes(n, k, policy), dtype=torch.uint8, device=dev),
-                "a": [torch.empty((panel_rows, k), dtype=torch.float32, device=dev) for _ in range(2)],
-                "ap": [torch.empty(packed_bytes(panel_rows, k, policy), dtype=torch.uint8, device=dev)
-                       for _ in range(2)],
-                "c": [torch.empty((panel_rows, n), dtype=torch.float32, device=dev) for _ in range(2)],
-            }
-        _host_ctx[key] = ctx
     with torch.cuda.device(dev):
-        cur = torch.cuda.current_stream()
-        s_in, s_out = ctx["s_in"], ctx["s_out"]
-        s_in.wait_stream(cur)
-        s_out.wait_stream(cur)
-        with torch.cuda.stream(s_in):
-            ctx["b"].copy_(b_host, non_blocking=True)
-            e_b = s_in.record_event()
-        cur.wait_event(e_b)
-        pack_b(ctx["b"], policy, out=ctx["bp"])
-        a_free = [None, None]   # compute finished reading a[i]
-        c_done = [None, None]   # copy-out finished reading c[i]
-        for p, r0 in enumerate(range(0, m, panel_rows)):
-            rows = min(panel_rows, m - r0)
-            i = p % 2
-            with torch.cuda.stream(s_in):
-                if a_free[i] is not None:
-                    s_in.wait_event(a_free[i])
-                ctx["a"][i][:rows].copy_(a_host[r0:r0 + rows], non_blocking=True)
-                e_a = s_in.record_event()
-            cur.wait_event(e_a)
-            pack_a(ctx["a"][i][:rows], policy, out=ctx["ap"][i])
-            a_free[i] = cur.record_event()
-            if c_done[i] is not None:
-                cur.wait_event(c_done[i])
-            sgemm_packed(ctx["ap"][i], ctx["bp"], rows, n, k, ctx["c"][i][:rows], policy=policy)
-            e_c = cur.record_event()
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(e_c)
-                c_host[r0:r0 + rows].copy_(ctx["c"][i][:rows], non_blocking=True)
-                c_done[i] = s_out.record_event()
-        cur.wait_stream(s_out)
+        st = load().tcec_sgemm_host(la, lb, lc, m, n, k, alpha, a_host.data_ptr(), lda, b_host.data_ptr(), ldb, beta,
+                                    c_host.data_ptr(), ldc, _policy(policy), int(panel_rows), _stream_ptr())
+    _check(st, "tcec_sgemm_host")
     return c_host
+
+
+# ---------------------------------------------------------------- several GPUs
+def comm_unique_id() -> bytes:
+    """Rank 0's communicator id (``tcec_comm_unique_id``), to be handed to every rank."""
+    buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+    _check(load().tcec_comm_unique_id(buf), "tcec_comm_unique_id")
+    return buf.raw
+
+
+def comm_init_rank(nranks: int, rank: int, uid: bytes) -> None:
+    """Creates this process's communicator on the current device (``tcec_comm_init_rank``)."""
+    if len(uid) != COMM_ID_BYTES:
+        raise ValueError("communicator id has the wrong size")
+    buf = ctypes.create_string_buffer(uid, COMM_ID_BYTES)
+    _check(load().tcec_comm_init_rank(int(nranks), int(rank), buf), "tcec_comm_init_rank")
+
+
+def comm_destroy() -> None:
+    _check(load().tcec_comm_destroy(), "tcec_comm_destroy")
+
+
+def _opt_mat(t: Optional[torch.Tensor]):
+    if t is None:
+        return ROW_MAJOR, 0, None
+    la, lda = _layout_ld(t)
+    return la, lda, t.data_ptr()
+
+
+def sgemm_column_shard(a: Optional[torch.Tensor], b_local: torch.Tensor, c_local: torch.Tensor, m: int, k: int, *,
+                       root: int = 0, alpha: float = 1.0, beta: float = 0.0, policy="fp16_ec") -> torch.Tensor:
+    """This rank's part of the column-sharded GEMM (``tcec_sgemm_column_shard``): ``a`` (m x k) is
+    needed on ``root`` only; ``b_local`` is k x n_local, ``c_local`` m x n_local, on the current device."""
+    _require_cuda_f32(b_local, c_local)
+    la, lda, ap = _opt_mat(a)
+    lb, ldb = _layout_ld(b_local)
+    lc, ldc = _layout_ld(c_local)
+    with torch.cuda.device(c_local.device):
+        st = load().tcec_sgemm_column_shard(root, la, lb, lc, m, b_local.shape[1], k, alpha, ap, lda, b_local.data_ptr(),
+                                            ldb, beta, c_local.data_ptr(), ldc, _policy(policy), _stream_ptr())
+    _check(st, "tcec_sgemm_column_shard")
+    return c_local
+
+
+def sgemm_column_shard_host(a_host: Optional[torch.Tensor], b_host: torch.Tensor, c_host: torch.Tensor, m: int, k: int,
+                            *, root: int = 0, alpha: float = 1.0, beta: float = 0.0, policy="fp16_ec",
+                            panel_rows: int = 2048) -> torch.Tensor:
+    """The same with host operands (``tcec_sgemm_column_shard_host``): copy-in, broadcast, GEMM and
+    copy-out pipelined in row panels; complete when the current stream has reached the end of it."""
+    _require_host_f32(b_host, c_host)
+    la, lda, ap = _opt_mat(a_host)
+    lb, ldb = _layout_ld(b_host)
+    lc, ldc = _layout_ld(c_host)
+    st = load().tcec_sgemm_column_shard_host(root, la, lb, lc, m, b_host.shape[1], k, alpha, ap, lda, b_host.data_ptr(),
+                                             ldb, beta, c_host.data_ptr(), ldc, _policy(policy), int(panel_rows),
+                                             _stream_ptr())
+    _check(st, "tcec_sgemm_column_shard_host")
+    return c_host
+
+
+def _parr(ctype, values):
+    return (ctype * len(values))(*values)
+
+
+def sgemm_multi(a: torch.Tensor, b_blocks: Sequence[torch.Tensor], c_blocks: Sequence[torch.Tensor], *,
+                alpha: float = 1.0, beta: float = 0.0, policy="fp16_ec") -> Sequence[torch.Tensor]:
+    """One process driving several GPUs (``tcec_sgemm_multi``): block i of B and C lives on its own
+    device, A on the device of block 0.  Returns when everything is queued on every device's current stream."""
+    devices = [t.device.index for t in c_blocks]
+    m, k = a.shape
+    la, lda = _layout_ld(a)
+    lays = [(_layout_ld(bb), _layout_ld(cc)) for bb, cc in zip(b_blocks, c_blocks)]
+    if len({(x[0][0], x[1][0]) for x in lays}) != 1:
+        raise ValueError("blocks must share their layouts")
+    lb, lc = lays[0][0][0], lays[0][1][0]
+    streams = [torch.cuda.current_stream(t.device).cuda_stream for t in c_blocks]
+    st = load().tcec_sgemm_multi(
+        len(devices), _parr(ctypes.c_int, devices), la, lb, lc, m, _parr(ctypes.c_int, [t.shape[1] for t in b_blocks]), k,
+        alpha, a.data_ptr(), lda, _parr(ctypes.c_void_p, [t.data_ptr() for t in b_blocks]),
+        _parr(ctypes.c_longlong, [x[0][1] for x in lays]), beta, _parr(ctypes.c_void_p, [t.data_ptr() for t in c_blocks]),
+        _parr(ctypes.c_longlong, [x[1][1] for x in lays]), _policy(policy), _parr(ctypes.c_void_p, streams))
+    _check(st, "tcec_sgemm_multi")
+    return c_blocks
+
+
+def sgemm_batched_multi(a_parts: Sequence[torch.Tensor], b_parts: Sequence[torch.Tensor],
+                        c_parts: Sequence[torch.Tensor], *, alpha: float = 1.0, beta: float = 0.0,
+                        policy="fp16_ec") -> Sequence[torch.Tensor]:
+    """A batch divided among several GPUs driven by one process (``tcec_sgemm_batched_multi``):
+    part i ([count_i, m, k] x [count_i, k, n]) lives on its own device; no collective."""
+    devices = [t.device.index for t in c_parts]
+    _, m, k = a_parts[0].shape
+    n = b_parts[0].shape[2]
+    la, lda = _layout_ld(a_parts[0])
+    lb, ldb = _layout_ld(b_parts[0])
+    lc, ldc = _layout_ld(c_parts[0])
+    streams = [torch.cuda.current_stream(t.device).cuda_stream for t in c_parts]
+    st = load().tcec_sgemm_batched_multi(
+        len(devices), _parr(ctypes.c_int, devices), la, lb, lc, m, n, k, alpha,
+        _parr(ctypes.c_void_p, [t.data_ptr() for t in a_parts]), lda, a_parts[0].stride(0),
+        _parr(ctypes.c_void_p, [t.data_ptr() for t in b_parts]), ldb, b_parts[0].stride(0), beta,
+        _parr(ctypes.c_void_p, [t.data_ptr() for t in c_parts]), ldc, c_parts[0].stride(0),
+        _parr(ctypes.c_int, [t.shape[0] for t in a_parts]), _policy(policy), _parr(ctypes.c_void_p, streams))
+    _check(st, "tcec_sgemm_batched_multi")
+    return c_parts
 
 
 def split(x: torch.Tensor, policy="fp16_ec"):
