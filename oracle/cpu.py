@@ -44,6 +44,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_gemm_f32.restype = None
     lib.oracle_errors.argtypes = [f32p, f64p, sz, f64p]
     lib.oracle_errors.restype = None
+    lib.oracle_set_num_threads.argtypes = [i]
+    lib.oracle_set_num_threads.restype = None
     lib.oracle_num_threads.argtypes = []
     lib.oracle_num_threads.restype = i
     _lib = lib
@@ -145,6 +147,18 @@ def errors(c: np.ndarray, ref: np.ndarray) -> dict:
     out = np.zeros(3, dtype=np.float64)
     load().oracle_errors(c, ref, c.size, out)
     return {"max_rel": float(out[0]), "fro_rel": float(out[1]), "max_abs": float(out[2])}
+
+
+def use_all_cores() -> int:
+    """Lets the host loops use every core of the machine, whatever the launcher put into
+    OMP_NUM_THREADS or the affinity mask (torchrun sets OMP_NUM_THREADS=1); returns the count."""
+    n = os.cpu_count() or 1
+    try:
+        os.sched_setaffinity(0, range(n))
+    except (AttributeError, OSError):
+        pass
+    load().oracle_set_num_threads(n)
+    return num_threads()
 
 
 def num_threads() -> int:

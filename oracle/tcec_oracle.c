@@ -247,6 +247,15 @@ void oracle_errors(const float* c, const double* ref, size_t count, double* out)
   out[2] = maxd;
 }
 
+/* Thread count of the host loops, set explicitly so that a launcher's OMP_NUM_THREADS does not decide it. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

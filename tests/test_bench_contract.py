@@ -28,3 +28,16 @@ def test_other_ranks_of_the_reference_arm_do_nothing():
                           "--steps", "1", "--warmup", "0", "--gpus", "2"], capture_output=True, text=True,
                          timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_reference_arm_uses_every_core_whatever_the_launcher_sets():
+    """Launched as torchrun launches it (OMP_NUM_THREADS=1, rank 0 of 2) the arm still runs the host
+    loop on all cores, on the multi-GPU workload's shape."""
+    env = dict(os.environ, RANK="0", WORLD_SIZE="2", OMP_NUM_THREADS="1")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                          "--large", "512", "768", "256", "--steps", "1", "--warmup", "0"], capture_output=True,
+                         text=True, timeout=300, cwd=ROOT, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["cpu_baseline"]["cores"] == os.cpu_count()
+    assert "M=512 N=768 K=256" in d["config"]["workload"] and d["n_gpus"] == 2 and d["scaling"] == "strong"
