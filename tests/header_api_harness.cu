@@ -137,4 +137,12 @@ int hdr_dump(int use, float* hi, float* lo, const float* src_rowmajor_32x32) {
   else dump_kernel<nvcuda::wmma::accumulator, half, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
   return (int)cudaGetLastError();
 }
+// the same for the op_mma tf32 fragments (m16n8k8)
+int hdr_dump_tf32(int use, float* hi, float* lo, const float* src_rowmajor_32x32) {
+  using Policy = typename tc::default_policy<tf32, tc::with_ec, tc::op_mma>::type;
+  if (use == 0) dump_kernel<nvcuda::wmma::matrix_a, tf32, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
+  else if (use == 1) dump_kernel<nvcuda::wmma::matrix_b, tf32, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
+  else dump_kernel<nvcuda::wmma::accumulator, tf32, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
+  return (int)cudaGetLastError();
+}
 }

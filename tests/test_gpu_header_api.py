@@ -30,6 +30,8 @@ def hdr():
     lib.hdr_matvec.restype = i
     lib.hdr_dump.argtypes = [i, p, p, p]
     lib.hdr_dump.restype = i
+    lib.hdr_dump_tf32.argtypes = [i, p, p, p]
+    lib.hdr_dump_tf32.restype = i
     return lib
 
 
@@ -168,6 +170,48 @@ def test_element_map_of_op_mma_half_fragments(hdr):
                         rr, e = (r // 2) % 2, r % 2
                         i, j = g + 8 * rr, 2 * t + e
                     assert h[lane, f * ne + r] == src[i + bm * rows, j + bn * cols], (use, lane, f, r)
+
+
+def test_element_map_of_op_mma_tf32_fragments(hdr):
+    """x(i) of the op_mma tf32 fragments follows the PTX m16n8k8 register order (reference
+    include/wmma_extension/detail/m16n8k8_tf32.hpp:68-112; accumulator as m16n8k8 float,
+    detail/m16n8k8.hpp:136-165): A x0..x3 = (r, c), (r+8, c), (r, c+4), (r+8, c+4) with r = lane/4,
+    c = lane%4; B x0, x1 = (k = lane%4, n = lane/4), (k+4, n); C x0..x3 = (r, 2c), (r, 2c+1), (r+8, 2c), (r+8, 2c+1)."""
+    src = (np.arange(32 * 32, dtype=np.float32)).reshape(32, 32) / 8.0  # exactly representable in tf32
+    for use, shape in ((0, (16, 8)), (1, (8, 8)), (2, (16, 8))):
+        rows, cols = shape
+        ne = rows * cols // 32
+        blocks_m, blocks_n = 32 // rows, 32 // cols
+        hi = torch.zeros(32, ne * blocks_m * blocks_n, device=DEV)
+        lo = torch.zeros_like(hi)
+        st = _t(src)
+        assert hdr.hdr_dump_tf32(use, hi.data_ptr(), lo.data_ptr(), st.data_ptr()) == 0
+        torch.cuda.synchronize()
+        h = hi.cpu().numpy()
+        for lane in range(32):
+            g, t = lane // 4, lane % 4
+            for f in range(blocks_m * blocks_n):
+                bm, bn = f % blocks_m, f // blocks_m
+                for r in range(ne):
+                    if use == 0:
+                        i, j = g + 8 * (r % 2), t + 4 * (r // 2)
+                    elif use == 1:
+                        i, j = t + 4 * r, g
+                    else:
+                        i, j = g + 8 * (r // 2), 2 * t + (r % 2)
+                    assert h[lane, f * ne + r] == src[i + bm * rows, j + bn * cols], (use, lane, f, r)
+        assert not lo.any()  # exactly representable values leave no residual
+
+
+def test_reference_vector_test_program_reports_no_error_on_these_headers():
+    """test/tcec/vector.cu of the reference, compiled unchanged against these headers: load_vector must
+    equal load_matrix_sync of the zero-padded matrix lane by lane (test/tcec/vector.cu:15-60) and
+    store_vector must give back the vector (:62-75); the program prints the errors, all must be zero."""
+    text = _run_reference_test_binary("reftest_vector.newhdr")
+    lane_errors = [float(x) for x in re.findall(r"^\[\d+\]\s+(\S+)\s*$", text, flags=re.M)]
+    store_errors = [float(x) for x in re.findall(r"^Error\s*:\s*(\S+)\s*$", text, flags=re.M)]
+    assert len(lane_errors) >= 32 * 8 and len(store_errors) >= 4, (len(lane_errors), len(store_errors))
+    assert max(lane_errors) == 0.0 and max(store_errors) == 0.0
 
 
 def _run_reference_test_binary(name):
