@@ -255,9 +255,10 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                loads its rows of A and half of B; bit-identical results).  -1 (default) = for
  *                the policies without error correction, where one product per K block leaves the
  *                kernel waiting on operands from L2 and the pair is 10-15 % faster (16384^3
- *                fp16: 812 vs 677-735 TFLOP/s); 0 = never; 1 = whenever it applies.  With error
- *                correction the pair is 4 % faster at 4096^3 but draws more power and is slower
- *                at the board's power cap, so the automatic choice leaves it off there.
+ *                fp16: 812 vs 677-735 TFLOP/s), and with error correction for calls below about
+ *                5000^3, which are over before the board reaches its power cap (2048^3: +8 %,
+ *                4096^3: +2 %; at the cap the pair draws more power per product and is 5 %
+ *                slower); 0 = never; 1 = whenever it applies.
  *   "reserve_sms" 0..64 (default 0): SMs the GEMM kernels do not occupy.  Their persistent CTAs take
  *                every register of an SM, so a communication kernel launched beside them can only
  *                run where the GEMM has no CTA.

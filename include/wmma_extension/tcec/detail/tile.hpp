@@ -1,11 +1,20 @@
-// Per-warp register tiles for mma.sync and their element <-> (row, column) maps.
+// Per-warp register tiles of the TCEC fragments and their element <-> (row, column) maps.
 //
-// One tile is the operand of one tensor-core step of the TCEC fragments: A is 16 x fk,
-// B is fk x fn, the accumulator 16 x fn, with fk = 16 or 8 (half), 8 (tf32) and fn = 8 or 16.
-// Register order is the one PTX documents for mma.sync.aligned.m16n8k16 / m16n8k8 (f16) and
-// m16n8k8 (tf32); a 16-wide tile is two n8 blocks back to back.  The reference keeps
-// these maps in include/wmma_extension/detail/m16n8k16.hpp:100-176, detail/m16n8k8.hpp:136-165
-// and detail/m16n8k8_tf32.hpp:68-112; element order of A/B/C tiles here is the same.
+// One tile is the operand of one tensor-core step: A is 16 x fk, B is fk x fn, the accumulator
+// 16 x fn, with fk = 16 or 8 (half), 8 (tf32) and fn = 8 or 16.
+//
+// op_mma: `tile` below, in the register order PTX documents for mma.sync.aligned.m16n8k16 /
+// m16n8k8 (f16) and m16n8k8 (tf32).  The reference keeps these maps in
+// include/wmma_extension/detail/m16n8k16.hpp:100-176, detail/m16n8k8.hpp:136-165 and
+// detail/m16n8k8_tf32.hpp:68-112; element order of A/B/C tiles here is the same.
+//
+// op_wmma: the tile IS nvcuda::wmma::fragment<Use, 16, 16, fk, T, Layout>, as in the reference
+// (include/wmma_extension/tcec/detail/policy.hpp:107-112), so sub_frag[] can be handed to
+// nvcuda::wmma::* and x(i) follows nvcuda's element order.  That order is not documented; the
+// maps below state what sm_80 and later do (the reference states the same facts in
+// detail/sm_80.hpp:95-173 and detail/sm_80_tf32.hpp:102-184) and a test compares them with
+// nvcuda::wmma::load_matrix_sync on the GPU it runs on.  Half A and B fragments hold every
+// element twice (registers x and x + 8).
 #ifndef TCEC_B200_DETAIL_TILE_HPP
 #define TCEC_B200_DETAIL_TILE_HPP
 #include "policy.hpp"
@@ -171,6 +180,107 @@ __device__ inline void tile_mma(tile<nvcuda::wmma::accumulator, 16, FN, 8, nvcud
           "r"(__float_as_uint(b.x[2 * nb + 1])), "f"(c.x[4 * nb + 0]), "f"(c.x[4 * nb + 1]),
           "f"(c.x[4 * nb + 2]), "f"(c.x[4 * nb + 3]));
   }
+}
+
+// ---------------------------------------------------------------- op_wmma: nvcuda fragments as tiles
+template <class Use, class T>
+struct wmma_element {
+  using type = T;
+};
+template <class T>
+struct wmma_element<nvcuda::wmma::accumulator, T> {
+  using type = float;
+};
+// nvcuda's A and B fragments need a layout; a TCEC fragment declared without one gets the usual
+// one (A row-major, B column-major).  Accumulators have none.
+template <class Use, class Layout>
+struct wmma_layout {
+  using type = Layout;
+};
+template <>
+struct wmma_layout<nvcuda::wmma::matrix_a, void> {
+  using type = nvcuda::wmma::row_major;
+};
+template <>
+struct wmma_layout<nvcuda::wmma::matrix_b, void> {
+  using type = nvcuda::wmma::col_major;
+};
+template <class Layout>
+struct wmma_layout<nvcuda::wmma::accumulator, Layout> {
+  using type = void;
+};
+
+// the tile type of a policy
+template <class Op, class Use, int FM, int FN, int FK, class T, class Layout>
+struct sub_tile {
+  using type = tile<Use, FM, FN, FK, T>;
+};
+template <class Use, int FK, class T, class Layout>
+struct sub_tile<op_wmma, Use, 16, 16, FK, T, Layout> {
+  using type = nvcuda::wmma::fragment<Use, 16, 16, FK, typename wmma_element<Use, T>::type,
+                                      typename wmma_layout<Use, Layout>::type>;
+};
+
+// rows, cols, register type and element map of a tile type
+template <class Tile>
+struct tile_traits;
+template <class Use, int FM, int FN, int FK, class T>
+struct tile_traits<tile<Use, FM, FN, FK, T>> {
+  using tile_t = tile<Use, FM, FN, FK, T>;
+  using storage_t = typename tile_t::storage_t;
+  static constexpr int rows = tile_t::rows, cols = tile_t::cols;
+  template <class F>
+  __device__ static void for_each(F f) {
+    tile_t::for_each(f);
+  }
+};
+template <class Use, int FK, class E, class L>
+struct tile_traits<nvcuda::wmma::fragment<Use, 16, 16, FK, E, L>> {
+  using tile_t = nvcuda::wmma::fragment<Use, 16, 16, FK, E, L>;
+  using storage_t = typename tile_t::storage_element_type;
+  static constexpr int rows = select_value<Use, 16, FK, 16>::value;
+  static constexpr int cols = select_value<Use, FK, 16, 16>::value;
+  static constexpr bool kTwice = std::is_same<E, half>::value;  // half A and B: every element in registers x and x + 8
+  // calls f(register index, row, column) for every register this lane holds
+  template <class F>
+  __device__ static void for_each(F f) {
+    const unsigned lane = lane_id(), g = lane >> 2, t = lane & 3;
+    if (std::is_same<Use, nvcuda::wmma::accumulator>::value) {
+#pragma unroll
+      for (unsigned x = 0; x < 8; ++x) f(x, g + 8 * ((x >> 1) & 1), 2 * t + (x & 1) + 8 * (x >> 2));
+    } else if (std::is_same<Use, nvcuda::wmma::matrix_a>::value) {
+      if (FK == 16) {
+#pragma unroll
+        for (unsigned x = 0; x < 8; ++x) {
+          f(x, g + 8 * ((x >> 1) & 1), 2 * t + (x & 1) + 8 * (x >> 2));
+          f(x + 8, g + 8 * ((x >> 1) & 1), 2 * t + (x & 1) + 8 * (x >> 2));
+        }
+      } else {
+#pragma unroll
+        for (unsigned x = 0; x < 4; ++x) f(x, g + 8 * (x & 1), t + 4 * (x >> 1));
+      }
+    } else {
+      if (FK == 16) {
+#pragma unroll
+        for (unsigned x = 0; x < 8; ++x) {
+          f(x, 2 * t + (x & 1) + 8 * ((x >> 1) & 1), g + 8 * (x >> 2));
+          f(x + 8, 2 * t + (x & 1) + 8 * ((x >> 1) & 1), g + 8 * (x >> 2));
+        }
+      } else {
+#pragma unroll
+        for (unsigned x = 0; x < 4; ++x) f(x, t + 4 * (x & 1), g + 8 * (x >> 1));
+      }
+    }
+  }
+};
+
+// d = a * b + c through nvcuda::wmma (d and c may be the same fragment)
+template <int FK, class T, class LA, class LB>
+__device__ inline void tile_mma(nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, FK, float>& d,
+                                const nvcuda::wmma::fragment<nvcuda::wmma::matrix_a, 16, 16, FK, T, LA>& a,
+                                const nvcuda::wmma::fragment<nvcuda::wmma::matrix_b, 16, 16, FK, T, LB>& b,
+                                const nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, FK, float>& c) {
+  nvcuda::wmma::mma_sync(d, a, b, c);
 }
 
 }  // namespace detail

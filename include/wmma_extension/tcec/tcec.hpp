@@ -47,7 +47,7 @@ template <class Use, int m, int n, int k, class T, class Layout = void,
           class Policy_ = typename mtk::wmma::tcec::detail::default_policy<T>::type>
 struct fragment
     : detail::corr_storage<
-          detail::tile<Use, Policy_::m, Policy_::n, Policy_::k, T>,
+          typename detail::sub_tile<typename Policy_::op, Use, Policy_::m, Policy_::n, Policy_::k, T, Layout>::type,
           (detail::select_value<Use, m, k, m>::value /
            detail::select_value<Use, Policy_::m, Policy_::k, Policy_::m>::value) *
               (detail::select_value<Use, k, n, n>::value /
@@ -55,8 +55,10 @@ struct fragment
           detail::has_ec<typename Policy_::error_correction>::value> {
   using Policy = Policy_;
   using element_type = float;
-  using sub_frag_t = detail::tile<Use, Policy::m, Policy::n, Policy::k, T>;
-  using storage_t = typename sub_frag_t::storage_t;
+  // op_mma: a register tile in PTX mma.sync order; op_wmma: nvcuda::wmma::fragment itself
+  using sub_frag_t = typename detail::sub_tile<typename Policy::op, Use, Policy::m, Policy::n, Policy::k, T, Layout>::type;
+  using tile_traits = detail::tile_traits<sub_frag_t>;
+  using storage_t = typename tile_traits::storage_t;
   static constexpr bool error_corrected = detail::has_ec<typename Policy::error_correction>::value;
   static constexpr int sub_frag_m = Policy::m;
   static constexpr int sub_frag_n = Policy::n;
@@ -65,8 +67,8 @@ struct fragment
                                         detail::select_value<Use, sub_frag_m, sub_frag_k, sub_frag_m>::value;
   static constexpr int num_sub_frag_n = detail::select_value<Use, k, n, n>::value /
                                         detail::select_value<Use, sub_frag_k, sub_frag_n, sub_frag_n>::value;
-  static_assert(detail::select_value<Use, m, k, m>::value % sub_frag_t::rows == 0 &&
-                    detail::select_value<Use, k, n, n>::value % sub_frag_t::cols == 0,
+  static_assert(detail::select_value<Use, m, k, m>::value % tile_traits::rows == 0 &&
+                    detail::select_value<Use, k, n, n>::value % tile_traits::cols == 0,
                 "fragment extents must be multiples of the policy's tile");
   static const unsigned num_elements = num_sub_frag_m * num_sub_frag_n * sub_frag_t::num_elements;
 
@@ -137,7 +139,7 @@ template <class MemLayout, class Use, class Layout, TCEC_TPARAMS, class Get>
 __device__ void load_with(TCEC_FRAG(Use, Layout) & frag, Get get, const unsigned ldm, const float mul,
                           const bool use_mul) {
   using F = TCEC_FRAG(Use, Layout);
-  using tile_t = typename F::sub_frag_t;
+  using tile_t = typename F::tile_traits;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
     for (int bm = 0; bm < F::num_sub_frag_m; bm++)
       for (int bn = 0; bn < F::num_sub_frag_n; bn++) {
@@ -213,7 +215,7 @@ template <class MemLayout, TCEC_TPARAMS, class Put>
 __device__ void store_with(Put put, const TCEC_FRAG(nvcuda::wmma::accumulator, void) & frag, const unsigned ldm,
                            const float mul, const bool use_mul) {
   using F = TCEC_FRAG(nvcuda::wmma::accumulator, void);
-  using tile_t = typename F::sub_frag_t;
+  using tile_t = typename F::tile_traits;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
     for (int bm = 0; bm < F::num_sub_frag_m; bm++)
       for (int bn = 0; bn < F::num_sub_frag_n; bn++) {
@@ -276,7 +278,7 @@ template <bool kFirstColumn, class Use, class Layout, TCEC_TPARAMS, class MEM_T>
 __device__ void load_vector_impl(TCEC_FRAG(Use, Layout) & frag, const MEM_T* const ptr, const float mul,
                                  const bool use_mul) {
   using F = TCEC_FRAG(Use, Layout);
-  using tile_t = typename F::sub_frag_t;
+  using tile_t = typename F::tile_traits;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
     if ((kFirstColumn ? j : i) != 0) return;
     const int nblk = kFirstColumn ? F::num_sub_frag_m : F::num_sub_frag_n;
@@ -305,7 +307,7 @@ template <bool kFirstColumn, TCEC_TPARAMS, class MEM_T>
 __device__ void store_vector_impl(MEM_T* const ptr, const TCEC_FRAG(nvcuda::wmma::accumulator, void) & frag,
                                   const float mul, const bool use_mul) {
   using F = TCEC_FRAG(nvcuda::wmma::accumulator, void);
-  using tile_t = typename F::sub_frag_t;
+  using tile_t = typename F::tile_traits;
   tile_t::for_each([&](unsigned r, unsigned i, unsigned j) {
     if ((kFirstColumn ? j : i) != 0) return;
     const int nblk = kFirstColumn ? F::num_sub_frag_m : F::num_sub_frag_n;

@@ -87,6 +87,47 @@ __global__ void dump_kernel(float* hi_out, float* lo_out, const float* src) {
   }
 }
 
+// Element map of the op_wmma sub-fragments against nvcuda::wmma::load_matrix_sync on the running GPU:
+// the same index-coded matrix is loaded both ways; *bad counts registers that differ.
+template <class Use, class T, class Layout, int FK>
+__global__ void wmma_map_kernel(int* bad) {
+  using Policy = tc::Policy<tc::op_wmma, tc::without_ec, 16, 16, FK>;
+  constexpr int R = tc::detail::select_value<Use, 16, FK, 16>::value;
+  constexpr int C = tc::detail::select_value<Use, FK, 16, 16>::value;
+  constexpr bool kAcc = std::is_same<Use, nvcuda::wmma::accumulator>::value;
+  constexpr bool kCol = std::is_same<Layout, nvcuda::wmma::col_major>::value;
+  using Elem = typename std::conditional<kAcc || !std::is_same<T, half>::value, float, half>::type;
+  __shared__ float src[16 * 16];
+  __shared__ Elem coded[16 * 16];
+  for (int e = threadIdx.x; e < R * C; e += 32) {
+    const int i = e / C, j = e % C;
+    const float v = static_cast<float>(e + 1);  // exactly representable in half and tf32
+    const int at = kCol ? i + j * R : i * C + j;
+    src[at] = v;
+    coded[at] = static_cast<Elem>(v);
+  }
+  __syncwarp();
+  const unsigned ldm = kCol ? R : C;
+  using L = typename std::conditional<kAcc, void, Layout>::type;
+  tc::fragment<Use, 16, 16, FK, T, L, Policy> frag;
+  using sub_t = typename decltype(frag)::sub_frag_t;
+  sub_t ref;
+  if constexpr (kAcc) {
+    tc::load_matrix_sync(frag, src, ldm, kCol ? nvcuda::wmma::mem_col_major : nvcuda::wmma::mem_row_major);
+    nvcuda::wmma::load_matrix_sync(ref, coded, ldm, kCol ? nvcuda::wmma::mem_col_major : nvcuda::wmma::mem_row_major);
+  } else {
+    tc::load_matrix_sync(frag, src, ldm);
+    nvcuda::wmma::load_matrix_sync(ref, coded, ldm);
+  }
+  static_assert(std::is_same<sub_t, nvcuda::wmma::fragment<Use, 16, 16, FK, typename sub_t::element_type, L>>::value,
+                "op_wmma sub-fragments are nvcuda::wmma fragments");
+  int n = 0;
+  for (unsigned i = 0; i < ref.num_elements; i++)
+    if (static_cast<float>(frag.sub_frag[0].x[i]) != static_cast<float>(ref.x[i])) ++n;
+  static_assert(decltype(frag)::num_elements == sub_t::num_elements, "one sub-fragment");
+  if (n) atomicAdd(bad, n);
+}
+
 template <class T, class EC, class OP>
 int launch(float* d, const float* a, const float* b, const float* c, int mode) {
   using Policy = typename tc::default_policy<T, EC, OP>::type;
@@ -135,6 +176,22 @@ int hdr_dump(int use, float* hi, float* lo, const float* src_rowmajor_32x32) {
   if (use == 0) dump_kernel<nvcuda::wmma::matrix_a, half, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
   else if (use == 1) dump_kernel<nvcuda::wmma::matrix_b, half, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
   else dump_kernel<nvcuda::wmma::accumulator, half, Policy, 32><<<1, 32>>>(hi, lo, src_rowmajor_32x32);
+  return (int)cudaGetLastError();
+}
+// number of registers of the op_wmma fragments that disagree with nvcuda::wmma::load_matrix_sync (all nine kinds)
+int hdr_wmma_map_mismatches(int* bad_dev) {
+  using namespace nvcuda::wmma;
+  wmma_map_kernel<matrix_a, half, row_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_a, half, col_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_b, half, row_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_b, half, col_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<accumulator, half, row_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<accumulator, half, col_major, 16><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_a, tf32, row_major, 8><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_a, tf32, col_major, 8><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_b, tf32, row_major, 8><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<matrix_b, tf32, col_major, 8><<<1, 32>>>(bad_dev);
+  wmma_map_kernel<accumulator, tf32, row_major, 8><<<1, 32>>>(bad_dev);
   return (int)cudaGetLastError();
 }
 // the same for the op_mma tf32 fragments (m16n8k8)

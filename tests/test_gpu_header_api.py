@@ -32,6 +32,8 @@ def hdr():
     lib.hdr_dump.restype = i
     lib.hdr_dump_tf32.argtypes = [i, p, p, p]
     lib.hdr_dump_tf32.restype = i
+    lib.hdr_wmma_map_mismatches.argtypes = [p]
+    lib.hdr_wmma_map_mismatches.restype = i
     return lib
 
 
@@ -170,6 +172,18 @@ def test_element_map_of_op_mma_half_fragments(hdr):
                         rr, e = (r // 2) % 2, r % 2
                         i, j = g + 8 * rr, 2 * t + e
                     assert h[lane, f * ne + r] == src[i + bm * rows, j + bn * cols], (use, lane, f, r)
+
+
+def test_op_wmma_sub_fragments_are_nvcuda_fragments_with_nvcuda_element_order(hdr):
+    """With the op_wmma policy the sub-fragments are nvcuda::wmma::fragment objects (reference
+    include/wmma_extension/tcec/detail/policy.hpp:107-112) and x(i) follows nvcuda's (undocumented)
+    register order (detail/sm_80.hpp:95-173, detail/sm_80_tf32.hpp:102-184): on the GPU the test runs
+    on, every register equals what nvcuda::wmma::load_matrix_sync puts there, for half and tf32,
+    A and B in both layouts, and the accumulator."""
+    bad = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert hdr.hdr_wmma_map_mismatches(bad.data_ptr()) == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
 
 
 def test_element_map_of_op_mma_tf32_fragments(hdr):

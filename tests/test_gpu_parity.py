@@ -442,6 +442,23 @@ def test_ragged_batch_shapes():
     tcec.device_status()
 
 
+def test_more_matrices_than_a_grid_dimension_holds():
+    """70 000 tiny matrices: the batch index of the split kernel is a grid dimension (65 535 at
+    most), so such a batch takes several launches; every matrix must still be right."""
+    if _free_gib() < 12:
+        pytest.skip("needs 12 GiB of free device memory")
+    g = torch.Generator(device=DEV).manual_seed(44)
+    nb = 70000
+    a = torch.randn((nb, 16, 16), generator=g, device=DEV)
+    b = torch.randn((nb, 16, 16), generator=g, device=DEV)
+    c = tcec.sgemm_strided_batched(a, b)
+    tcec.device_status()
+    exact = torch.matmul(a.double(), b.double())
+    err = ((c.double() - exact).abs().amax(dim=(1, 2)) / exact.abs().amax(dim=(1, 2))).max().item()
+    assert err < 1e-6
+    tcec.destroy()  # gives the 4.6 GB workspace back
+
+
 def test_packed_entry_points_match_plain_call():
     rng = np.random.default_rng(42)
     m, n, k = 384, 300, 200

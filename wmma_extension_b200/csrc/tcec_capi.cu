@@ -187,8 +187,16 @@ __global__ void split_flat_kernel(const float* __restrict__ in, float* hi, float
 
 template <bool T, bool E>
 void launch_split(const SplitParams& sp, int batch, cudaStream_t stream) {
-  dim3 grid(sp.nkb, sp.row_blocks, batch);
-  tcec_split_panels_kernel<T, E><<<grid, 256, 0, stream>>>(sp);
+  // the batch index is the grid's z dimension (at most 65535): larger batches go in several launches
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    SplitParams part = sp;
+    const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
+    if (part.src_array) part.src_array += b0;
+    else part.src += static_cast<long long>(b0) * part.batch_stride;
+    part.panels += static_cast<long long>(b0) * part.panels_batch_stride;
+    dim3 grid(part.nkb, part.row_blocks, nb);
+    tcec_split_panels_kernel<T, E><<<grid, 256, 0, stream>>>(part);
+  }
 }
 
 template <int BN, bool T, bool E>
@@ -266,9 +274,12 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
   const int sms = st->sm_count - reserve > 1 ? st->sm_count - reserve : 1;
   const bool tf32 = policy_tf32(policy), ec = policy_ec(policy);
   // One product per K block makes the kernel wait on operands from L2, which a CTA pair halves
-  // for B: measured 10-15 % faster there, and no faster (slower at the power cap) with three products.
+  // for B: measured 10-15 % faster there.  With three products the pair is faster only while the
+  // clocks are high, i.e. for calls too short to reach the board's power cap (2048^3: +8 %,
+  // 4096^3: +2 %; 16384^3 back to back: -5 %), so the automatic choice takes it below ~5000^3.
+  const double flops = 2.0 * m * static_cast<double>(n) * k * batch;
   const bool want_pair = !ex.force_one_sm && !ex.row_ready && !ex.sched &&
-                         (opt.cta_pair == 1 || (opt.cta_pair == -1 && !ec));
+                         (opt.cta_pair == 1 || (opt.cta_pair == -1 && (!ec || flops <= 2.5e11)));
   if (want_pair && s.tile_n == 256 && m > 128) {
     // CTA pairs: 256 x 256 tiles, grid of up to sms/2 clusters of two CTAs
     gp.tiles_m = (m + 255) / 256;
@@ -286,6 +297,7 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
     return TCEC_OK;
   }
   const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
+  if (ntiles > 0x7fffffffll) return TCEC_ERR_UNSUPPORTED;  // tile indices are 32-bit
   int grid = static_cast<int>(ntiles < sms ? ntiles : sms);
   if (ex.sched) {
     // counters shared with other launches of the same problem; the caller zeroes them
@@ -422,8 +434,13 @@ int scale_only(float beta, float* c, float* const* c_array, long long ldc, long 
                int n, int lc, int batch, cudaStream_t stream) {
   if (beta == 1.f) return TCEC_OK;
   const int inner = lc == TCEC_COL_MAJOR ? m : n, outer = lc == TCEC_COL_MAJOR ? n : m;
-  dim3 grid((inner + 255) / 256, outer < 65535 ? outer : 65535, batch);
-  scale_c_kernel<<<grid, 256, 0, stream>>>(c, c_array, ldc, stride_c, m, n, lc == TCEC_COL_MAJOR, beta);
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
+    dim3 grid((inner + 255) / 256, outer < 65535 ? outer : 65535, nb);
+    scale_c_kernel<<<grid, 256, 0, stream>>>(c_array ? nullptr : c + static_cast<long long>(b0) * stride_c,
+                                             c_array ? c_array + b0 : nullptr, ldc, stride_c, m, n, lc == TCEC_COL_MAJOR,
+                                             beta);
+  }
   TCEC_CUDA(cudaGetLastError());
   return TCEC_OK;
 }
@@ -444,7 +461,6 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
     if (lda < (la == TCEC_ROW_MAJOR ? k : m)) return TCEC_ERR_INVALID_ARGUMENT;
     if (ldb < (lb == TCEC_ROW_MAJOR ? n : k)) return TCEC_ERR_INVALID_ARGUMENT;
   }
-  if (batch > 65535) return TCEC_ERR_UNSUPPORTED;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   // State is looked up (and a workspace grown) under the mutex; the launches run without it.

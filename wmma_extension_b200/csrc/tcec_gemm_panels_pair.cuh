@@ -37,6 +37,9 @@ struct GemmPairCfg {
   static constexpr int SMEM_BYTES = NST * STAGE_BYTES + 8 * kEpiBufBytes + 1024;
   static constexpr int TMEM_COLS = kEc ? 512 : 256;
   static constexpr int THREADS = 384;
+  // as in the one-SM kernel: the control warpgroup hands registers to the two epilogue warpgroups
+  static constexpr int REGS_CONTROL = 40, REGS_EPILOGUE = 232;
+  static_assert(128 * REGS_CONTROL + 256 * REGS_EPILOGUE <= THREADS * 168, "register shares");
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
 };
 
@@ -99,6 +102,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   const RingBarriers ring{bar_full, bar_empty};
 
   if (warp < 4) {
+    setmaxnreg_dec<Cfg::REGS_CONTROL>();
     if (warp == 0) {
       // ---------------------------------------------------------- producer (each CTA, own panels)
       if (lane == 0) {
@@ -185,6 +189,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     }
   } else {
     // ------------------------------------------------------------ epilogue (each CTA, its 128 rows)
+    setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     const int ew = warp - 4;
     const int q = warp & 3;
     const int colbase = (ew >> 2) * 128;
@@ -205,7 +210,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           break;
         }
         tc_fence_after();
-        promote_main_chunk<false>(acc, tmem_main + lane_addr + colbase, c == 0);
+        promote_main_chunk<true>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(main_free_leader);
