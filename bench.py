@@ -21,8 +21,8 @@ Throughput is FP32-equivalent: 2*M*N*K flop per GEMM.
 
 --impl reference times the reference's CPU path, its FP64 host check loop
 (test/tcec/batch_gemm.cu:561-575), ported in oracle/tcec_oracle.c, on a bounded row sample of the
-same workload with all host cores.  --only kernel runs nothing but the headline GEMM of N = 1
-(the command the profiler captures are made with).
+same workload with all host cores.  --only kernel runs nothing but the headline GEMM of N = 1,
+--only batched nothing but the batched configuration (the commands the profiler captures are made with).
 """
 import argparse
 import json
@@ -313,7 +313,7 @@ def sampled_accuracy(torch, np, cpu, a_rows, b_dev, c_rows):
 
 def batched_extra(torch, tcec, sharded, peaks, args, rank, world, device, dist_on):
     """8192 independent 256^3 products, N(0,1), batch-sharded (no collective); strong scaling."""
-    nb, bs = 8192, 256
+    nb, bs = args.batched, 256
     first, count = sharded.batch_shard(nb, rank, world)
     g = torch.Generator(device=device)
     g.manual_seed(4000 + rank)
@@ -339,7 +339,7 @@ def batched_extra(torch, tcec, sharded, peaks, args, rank, world, device, dist_o
 # DRAM traffic of one launch of tcec_gemm_panels_kernel<256,fp16,ec> on M = N = K = size, from ncu captures
 # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/): C is written once, A's panels are read about
 # once per pass, and B's panels once per group of 2048 rows of A, because neither operand fits the L2.
-TRAFFIC_POINTS = {6144: 1.126e9}
+TRAFFIC_POINTS = {6144: 1.130e9, 8192: 2.535e9, 16384: 37.2e9}
 
 
 def panel_gemm_traffic(size):
@@ -362,6 +362,10 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
     from oracle import cpu, ref
 
     rank, world, dist_on = 0, 1, False
+    if args.only == "batched":
+        print(json.dumps({"metric": METRIC, "n_gpus": 1, "steps": args.steps,
+                          "batched_256": batched_extra(torch, tcec, sharded, peaks, args, 0, 1, device, False)}), flush=True)
+        return
     size = args.size
     m = n = k = size
     policy = "fp16_ec"
@@ -710,8 +714,10 @@ def main():
     ap.add_argument("--large", type=int, nargs=3, default=list(LARGE), metavar=("M", "N", "K"),
                     help="shape of the column-sharded workload")
     ap.add_argument("--panel-rows", type=int, default=2048)
-    ap.add_argument("--only", default="", choices=["", "kernel"],
-                    help="kernel: nothing but the headline GEMM of one GPU (for profiler captures)")
+    ap.add_argument("--batched", type=int, default=8192, help="matrices of the batched 256^3 configuration")
+    ap.add_argument("--only", default="", choices=["", "kernel", "batched"],
+                    help="kernel: nothing but the headline GEMM of one GPU; batched: nothing but the batched "
+                         "configuration (the commands of the profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
