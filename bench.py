@@ -368,7 +368,7 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
         return
     size = args.size
     m = n = k = size
-    policy = "fp16_ec"
+    policy = args.policy if args.only == "kernel" else "fp16_ec"
     a = make_uniform(torch, device, m, k, seed=3)
     b = make_uniform(torch, device, k, n, seed=1003)
     c = torch.empty((m, n), dtype=torch.float32, device=device)
@@ -398,6 +398,7 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
             "data": "synthetic", "config": bench_config(1, size, tuple(args.large), args.panel_rows),
             "clocks": clocks, "gpu_launches": 3 * args.steps}  # split A, split B, GEMM
     line["config"]["promote_k"] = tcec.get_option("promote_k")
+    line["config"]["policy"] = policy
     if args.only == "kernel":
         print(json.dumps(line), flush=True)
         return
@@ -714,6 +715,8 @@ def main():
     ap.add_argument("--large", type=int, nargs=3, default=list(LARGE), metavar=("M", "N", "K"),
                     help="shape of the column-sharded workload")
     ap.add_argument("--panel-rows", type=int, default=2048)
+    ap.add_argument("--policy", default="fp16_ec", choices=["fp16_ec", "tf32_ec", "fp16_no_ec", "tf32_no_ec"],
+                    help="with --only kernel: the policy of the GEMM")
     ap.add_argument("--batched", type=int, default=8192, help="matrices of the batched 256^3 configuration")
     ap.add_argument("--only", default="", choices=["", "kernel", "batched"],
                     help="kernel: nothing but the headline GEMM of one GPU; batched: nothing but the batched "
