@@ -259,6 +259,10 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                5000^3, which are over before the board reaches its power cap (2048^3: +8 %,
  *                4096^3: +2 %; at the cap the pair draws more power per product and is 5 %
  *                slower); 0 = never; 1 = whenever it applies.
+ *   "tail_halves" 1 (default) = when the last wave of 256 x 256 tiles would occupy at most half of the
+ *                SM pairs, the CTA-pair kernel cuts those tiles into 256 x 128 halves taken by
+ *                different pairs, so the wave lasts half as long; 0 = whole tiles only.  Same
+ *                results bit for bit.
  *   "reserve_sms" 0..64 (default 0): SMs the GEMM kernels do not occupy.  Their persistent CTAs take
  *                every register of an SM, so a communication kernel launched beside them can only
  *                run where the GEMM has no CTA.

@@ -34,11 +34,13 @@ def _defaults():
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
     tcec.set_option("cta_pair", -1)
+    tcec.set_option("tail_halves", 1)
     yield
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
     tcec.set_option("cta_pair", -1)
+    tcec.set_option("tail_halves", 1)
 
 
 # ---------------------------------------------------------------- split (bit-exact)
@@ -291,6 +293,40 @@ def test_cta_pair_kernel_is_bit_identical(shape, policy):
     ab = _t(rng.standard_normal((5, 150, 96)).astype(np.float32))
     bb = _t(rng.standard_normal((5, 96, 260)).astype(np.float32))
     tcec.set_option("cta_pair", 0)
+    want = tcec.sgemm_strided_batched(ab, bb, policy=policy)
+    tcec.set_option("cta_pair", 1)
+    got = tcec.sgemm_strided_batched(ab, bb, policy=policy)
+    tcec.device_status()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("shape,policy", [((4096, 4096, 256), "fp16_ec"), ((4096, 3990, 96), "tf32_ec"),
+                                          ((1024, 1024, 512), "fp16_no_ec"), ((2300, 2100, 160), "tf32_no_ec"),
+                                          ((300, 130, 64), "fp16_ec")])
+def test_half_width_tiles_of_the_last_wave_are_bit_identical(shape, policy):
+    """An underfilled last wave of the CTA-pair kernel runs as 256 x 128 halves (whole tiles first,
+    then halves: 4096 x 4096 is 222 whole tiles and 68 halves on 74 pairs); every element of C is
+    the same as with whole tiles only, and as from the one-SM kernel."""
+    m, n, k = shape
+    rng = np.random.default_rng(900 + m + n + k)
+    a = _t(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = _t(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    tcec.set_option("path", 1)
+    tcec.set_option("cta_pair", 1)
+    out = {}
+    for halves in (0, 1):
+        tcec.set_option("tail_halves", halves)
+        c = torch.full((m + 1, n + 3), float("nan"), dtype=torch.float32, device="cuda")
+        tcec.sgemm(a, b, c[:m, :n], policy=policy)
+        tcec.device_status()
+        assert torch.isnan(c[m:, :]).all() and torch.isnan(c[:, n:]).all()
+        out[halves] = c[:m, :n].clone()
+    assert torch.equal(out[0], out[1])
+    tcec.set_option("cta_pair", 0)
+    assert torch.equal(tcec.sgemm(a, b, policy=policy), out[1])
+    # a batch whose last wave is underfilled: 80 matrices of one pair tile each on 74 pairs
+    ab = _t(rng.standard_normal((80, 256, 64)).astype(np.float32))
+    bb = _t(rng.standard_normal((80, 64, 256)).astype(np.float32))
     want = tcec.sgemm_strided_batched(ab, bb, policy=policy)
     tcec.set_option("cta_pair", 1)
     got = tcec.sgemm_strided_batched(ab, bb, policy=policy)

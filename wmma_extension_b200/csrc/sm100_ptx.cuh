@@ -270,6 +270,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
   return r;
 }
+// Raises the abort word of this CTA and of the other CTA of its pair (same shared-memory offset),
+// so that the peer's bounded waits end at their next look at the word instead of running out one by one.
+__device__ __forceinline__ void raise_abort_pair(uint32_t* abort_flag) {
+  *abort_flag = 1;
+  const uint32_t peer = map_to_cta(smem_u32(abort_flag), cluster_ctarank() ^ 1u);
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1u) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }

@@ -284,8 +284,15 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
     // CTA pairs: 256 x 256 tiles, grid of up to sms/2 clusters of two CTAs
     gp.tiles_m = (m + 255) / 256;
     const long long npair_tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
+    if (npair_tiles > 0x3fffffffll) return TCEC_ERR_UNSUPPORTED;  // work items are 32-bit
     const int max_pairs = sms / 2 > 1 ? sms / 2 : 1;
-    const int grid = 2 * static_cast<int>(npair_tiles < max_pairs ? npair_tiles : max_pairs);
+    // A last wave that fills at most half of the pairs is done in half-width tiles: twice as many
+    // work items, each half as long (4096^3: 256 tiles on 74 pairs, 3.46 -> 3.5 waves instead of 4).
+    const int tail = static_cast<int>(npair_tiles % max_pairs);
+    gp.narrow_from = static_cast<int>(npair_tiles);
+    if (opt.tail_halves && tail > 0 && 2 * tail <= max_pairs) gp.narrow_from -= tail;
+    const long long nwork = 2 * npair_tiles - gp.narrow_from;
+    const int grid = 2 * static_cast<int>(nwork < max_pairs ? nwork : max_pairs);
     if (tf32 && ec)
       tcec_gemm_panels_pair_kernel<true, true><<<grid, 384, GemmPairCfg<true, true>::SMEM_BYTES, stream>>>(gp);
     else if (tf32)
@@ -796,6 +803,7 @@ const OptionEntry kOptions[] = {
     {"promote_k", &Options::promote_k, -1, 0x7fffffff, any_value},
     {"tile_n", &Options::tile_n, 0, 256, tile_value},
     {"cta_pair", &Options::cta_pair, -1, 1, any_value},
+    {"tail_halves", &Options::tail_halves, 0, 1, any_value},
     {"path", &Options::path, 0, 2, any_value},
     {"store_turn", &Options::store_turn, 0, 1, any_value},
     {"reserve_sms", &Options::reserve_sms, 0, 64, any_value},

@@ -274,7 +274,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmFusedCfg<kEc>::T
       }
     }
     if (!ok) {
-      abort_flag = 1;
+      raise_abort_pair(&abort_flag);
       if (lane == 0) atomicCAS(p.status, 0, kErrProducerWait);
     }
   } else if (warp < 4) {
@@ -318,7 +318,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmFusedCfg<kEc>::T
         }
       }
       if (!ok) {
-        abort_flag = 1;
+        raise_abort_pair(&abort_flag);
         atomicCAS(p.status, 0, kErrProducerWait);
         for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
           if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_landed[q]), (armed_parity >> q) & 1);
@@ -341,7 +341,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmFusedCfg<kEc>::T
         }
       }
       if (!ok) {
-        abort_flag = 1;
+        raise_abort_pair(&abort_flag);
         atomicCAS(p.status, 0, kErrMmaWait);
       }
     } else if (lane == 0 && leader && (warp == 1 || (kEc && warp == 2))) {
@@ -457,7 +457,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmFusedCfg<kEc>::T
     }
     if (p.c_tma && lane == 0) bulk_wait_group<0>();  // this lane's stores are complete before the CTA ends
     if (!ok) {
-      abort_flag = 1;
+      raise_abort_pair(&abort_flag);
       if (lane == 0) atomicCAS(p.status, 0, kErrEpilogueWait);
     }
   }

@@ -18,6 +18,12 @@
 //   main_full / corr_full   likewise committed to both CTAs; each CTA drains its own TMEM
 //   main_free / corr_free   leader's barriers: 8 local epilogue warps + 8 remote arrives
 // Both CTAs meet at a cluster barrier after set-up and before exit.
+//
+// Work items: pair tiles below `p.narrow_from` are whole 256 x 256 tiles; every pair tile from
+// there on is cut into two 256 x 128 halves that different pairs take (the host does this to the
+// tiles of an underfilled last wave, which then lasts half as long).  A half is one 128-row B
+// panel of which each CTA loads its 64 rows (the first or second 4 KB of the panel), multiplied
+// with N = 128; every element of C still sees the same products in the same order.
 #pragma once
 #include "sm100_ptx.cuh"
 #include "tcec_gemm_panels.cuh"
@@ -43,6 +49,23 @@ struct GemmPairCfg {
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
 };
 
+struct PairWork {
+  TileCoord tc;
+  int half;  // -1: the whole pair tile; 0 / 1: its left / right 128 columns
+};
+__device__ __forceinline__ PairWork decode_pair_work(int w, int narrow_from, int tiles_m, int tiles_n, int group_m) {
+  PairWork r;
+  if (w < narrow_from) {
+    r.tc = decode_tile(w, tiles_m, tiles_n, group_m);
+    r.half = -1;
+  } else {
+    const int h = w - narrow_from;
+    r.tc = decode_tile(narrow_from + (h >> 1), tiles_m, tiles_n, group_m);
+    r.half = h & 1;
+  }
+  return r;
+}
+
 // p.tiles_m counts 256-row pair tiles here.
 template <bool kTf32, bool kEc>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
@@ -62,6 +85,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   const bool leader = (rank == 0);
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int ntiles = p.tiles_m * p.tiles_n * p.batch;
+  const int narrow_from = p.narrow_from < ntiles ? p.narrow_from : ntiles;
+  const int nwork = narrow_from + 2 * (ntiles - narrow_from);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
@@ -97,7 +122,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   im.b_hi16 = Cfg::A_BYTES >> 4;
   im.b_lo16 = (Cfg::A_BYTES + kPanelBytes) >> 4;
   im.idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
-  const StridedTiles tiles{pair, npairs, ntiles};
+  im.idesc_narrow = umma_idesc(kTf32 ? 2u : 0u, 256, BN / 2);
+  im.narrow_from = narrow_from;
+  const StridedTiles tiles{pair, npairs, nwork};
   const KWalk walk{p.nkb, p.promo};
   const RingBarriers ring{bar_full, bar_empty};
 
@@ -108,12 +135,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       if (lane == 0) {
         uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0, it = 0;
         bool ok = true;
-        for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-          const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+        for (int w = pair; w < nwork && ok; w += npairs) {
+          const PairWork pw = decode_pair_work(w, narrow_from, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+          const TileCoord tc = pw.tc;
+          const bool narrow = pw.half >= 0;
           const uint8_t* pa = p.panels_a + tc.b * p.panels_a_batch_stride +
                               static_cast<size_t>(tc.mt * 2 + rank) * p.nkb * Cfg::A_BYTES;
+          // whole tile: this CTA's 128-row panel of the tile's two; half: its 64 rows of the half's one panel
           const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
-                              static_cast<size_t>(tc.nt * 2 + rank) * p.nkb * Cfg::B_BYTES;
+                              static_cast<size_t>(tc.nt * 2 + (narrow ? pw.half : static_cast<int>(rank))) * p.nkb *
+                                  Cfg::B_BYTES +
+                              (narrow ? rank * (kPanelBytes / 2) : 0u);
           for (int kb = 0; kb < p.nkb; ++kb, ++it) {
             if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp, 128)) {
               ok = false;
@@ -129,11 +161,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
             }
             const uint32_t full = smem_u32(&bar_full[s]);
             const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
-            mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+            mbar_arrive_expect_tx(full, narrow ? Cfg::A_BYTES + Cfg::B_BYTES / 2 : Cfg::STAGE_BYTES);
             armed |= 1u << s;
             armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
             bulk_load(dst, pa + static_cast<size_t>(kb) * Cfg::A_BYTES, Cfg::A_BYTES, full);
-            bulk_load(dst + Cfg::A_BYTES, pb + static_cast<size_t>(kb) * Cfg::B_BYTES, Cfg::B_BYTES, full);
+            const uint8_t* srcb = pb + static_cast<size_t>(kb) * Cfg::B_BYTES;
+            if (!narrow) {
+              bulk_load(dst + Cfg::A_BYTES, srcb, Cfg::B_BYTES, full);
+            } else {
+#pragma unroll
+              for (int h = 0; h < Cfg::NP; ++h)  // hi (+ lo): each image keeps its place in the stage
+                bulk_load(dst + Cfg::A_BYTES + h * kPanelBytes, srcb + h * kPanelBytes, kPanelBytes / 2, full);
+            }
             if (++s == static_cast<uint32_t>(NST)) {
               s = 0;
               ph ^= 1;
@@ -141,7 +180,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           }
         }
         if (!ok) {
-          abort_flag = 1;
+          raise_abort_pair(&abort_flag);
           atomicCAS(p.status, 0, kErrProducerWait);
           for (uint32_t q = 0; q < static_cast<uint32_t>(NST); ++q)
             if (armed & (1u << q)) mbar_wait_plain(smem_u32(&bar_full[q]), (armed_parity >> q) & 1);
@@ -153,7 +192,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           // -------------------------------------------------------- peer: relay "my stage landed"
           uint32_t s = 0, ph = 0, it = 0;
           bool ok = true;
-          for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+          for (int w = pair; w < nwork && ok; w += npairs) {
             for (int kb = 0; kb < p.nkb; ++kb, ++it) {
               if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
                 ok = false;
@@ -167,7 +206,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
             }
           }
           if (!ok) {
-            abort_flag = 1;
+            raise_abort_pair(&abort_flag);
             atomicCAS(p.status, 0, kErrMmaWait);
           }
         } else {
@@ -200,8 +239,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     const uint32_t corr_free_leader = map_to_cta(smem_u32(&bar_corr_free), 0);
     uint32_t chunk = 0, tcount = 0;
     bool ok = true;
-    for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
-      const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+    for (int w = pair; w < nwork && ok; w += npairs, ++tcount) {
+      // a half tile has no columns for the second warpgroup: it only keeps the barriers' counts
+      const bool idle = w >= narrow_from && colbase != 0;
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
       float acc[128];
       for (int c = 0; c < nchunks; ++c, ++chunk) {
@@ -210,7 +250,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           break;
         }
         tc_fence_after();
-        promote_main_chunk<true>(acc, tmem_main + lane_addr + colbase, c == 0);
+        if (!idle) promote_main_chunk<true>(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(main_free_leader);
@@ -222,29 +262,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           break;
         }
         tc_fence_after();
-      }
-      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
-      const int col0 = tc.nt * BN + colbase;
-      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
-      if constexpr (kEc) {
-        fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
+        if (!idle) fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(corr_free_leader);
       }
+      if (idle) continue;
+      // Where the tile lies is worked out only now: nothing but the running sums stays live across
+      // the drains above, which need every register for their loads in flight.
+      const PairWork pw = decode_pair_work(w, narrow_from, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
+      const TileCoord tc = pw.tc;
+      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
+      const int col0 = tc.nt * BN + (pw.half >= 0 ? pw.half * 128 : colbase);
       StoreTarget st;
       st.cbase = cbase;
       st.ldc = p.ldc;
       st.M = p.M;
       st.N = p.N;
       st.col_major = p.c_col_major;
-      st.vec_ok = vec_ok;
+      st.vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
       st.alpha = p.alpha;
       st.beta = p.beta;
-      store_warp_block(acc, tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32, col0, st, reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
+      store_warp_block(acc, tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32, col0, st,
+                       reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
     }
     if (!ok) {
-      abort_flag = 1;
+      raise_abort_pair(&abort_flag);
       if (lane == 0) atomicCAS(p.status, 0, kErrEpilogueWait);
     }
   }

@@ -21,6 +21,10 @@ struct OperandImage {
   uint32_t b_hi16;
   uint32_t b_lo16;
   uint32_t idesc;      // instruction descriptor (type, M, N)
+  // Work items numbered `narrow_from` and above are half-width tiles and use `idesc_narrow`
+  // (same type and M, half the N); kernels without such items leave the defaults.
+  int narrow_from = 0x7fffffff;
+  uint32_t idesc_narrow = 0;
 };
 
 // How K is cut.
@@ -124,6 +128,7 @@ __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWal
     const int tile = tiles.next(abortp);
     if (tile == kNoMoreTiles) break;
     if (tile == kTileWaitFailed) return false;
+    const uint32_t idesc = tile >= im.narrow_from ? im.idesc_narrow : im.idesc;
     int left_in_chunk = 0;  // K blocks still to issue in the current chunk
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
@@ -142,7 +147,7 @@ __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWal
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_main, im.dconst | (a16 + 16 * j), im.dconst | (a16 + im.b_hi16 + 16 * j),
-                                   im.idesc, (first_in_chunk && j == 0) ? 0u : 1u);
+                                   idesc, (first_in_chunk && j == 0) ? 0u : 1u);
       }
       if (--left_in_chunk == 0) {
         umma_commit_to<kPair>(smem_u32(bar_main_full));
@@ -171,6 +176,7 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
     const int tile = tiles.next(abortp);
     if (tile == kNoMoreTiles) break;
     if (tile == kTileWaitFailed) return false;
+    const uint32_t idesc = tile >= im.narrow_from ? im.idesc_narrow : im.idesc;
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
       if (kb == 0) {
@@ -184,11 +190,11 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_corr, im.dconst | (c16 + im.a_lo16 + 16 * j),
-                                   im.dconst | (c16 + im.b_hi16 + 16 * j), im.idesc, (kb == 0 && j == 0) ? 0u : 1u);
+                                   im.dconst | (c16 + im.b_hi16 + 16 * j), idesc, (kb == 0 && j == 0) ? 0u : 1u);
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_corr, im.dconst | (c16 + 16 * j), im.dconst | (c16 + im.b_lo16 + 16 * j),
-                                   im.idesc, 1u);
+                                   idesc, 1u);
       }
       umma_commit_to<kPair>(smem_u32(&ring.empty[s]));
       if (++s == static_cast<uint32_t>(NST)) {
@@ -205,7 +211,8 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
 // writes TMEM when the CTA releases it.
 template <bool kPair>
 __device__ __forceinline__ void mma_thread_gave_up(uint32_t* abort_flag, int* status, int code, uint64_t* bar_drain) {
-  *abort_flag = 1;
+  if constexpr (kPair) raise_abort_pair(abort_flag);
+  else *abort_flag = 1;
   atomicCAS(status, 0, code);
   umma_commit_to<kPair>(smem_u32(bar_drain));
   mbar_wait_plain(smem_u32(bar_drain), 0);

@@ -235,6 +235,28 @@ struct Lane {
   StepState* ss = nullptr;
 };
 
+// One packed row panel of A from the root's buffer into every other lane's, in place, on the
+// communication streams.  One process driving several devices issues its ncclBroadcast calls
+// inside one group (ncclGroupStart / ncclGroupEnd), which is closed on every path out.
+int broadcast_panel(std::vector<Lane>& lanes, const Panel& pn, int root) {
+  const bool group = lanes.size() > 1;
+  if (group) TCEC_NCCL(g_nccl.GroupStart());
+  int rc = TCEC_OK;
+  for (Lane& ln : lanes) {
+    if (cudaSetDevice(ln.device) != cudaSuccess) {
+      rc = TCEC_ERR_CUDA;
+      break;
+    }
+    uint8_t* buf = static_cast<uint8_t*>(ln.ss->packed_a.ptr) + pn.offset;
+    if (g_nccl.Broadcast(buf, buf, pn.bytes, ncclUint8, root, ln.comm, ln.ss->s_comm) != ncclSuccess) {
+      rc = TCEC_ERR_COMM;
+      break;
+    }
+  }
+  if (group && g_nccl.GroupEnd() != ncclSuccess && rc == TCEC_OK) rc = TCEC_ERR_COMM;
+  return rc;
+}
+
 int check_shard_args(int la, int lb, int lc, int m, int k, int policy) {
   if (bad_layout(la) || bad_layout(lb) || bad_layout(lc) || m < 0 || k < 0 || policy < 0 || policy > 3)
     return TCEC_ERR_INVALID_ARGUMENT;
@@ -293,13 +315,8 @@ int column_step_device(std::vector<Lane>& lanes, int nranks, int root, int la, i
       }
     }
     if (nranks > 1) {
-      if (lanes.size() > 1) TCEC_NCCL(g_nccl.GroupStart());
-      for (Lane& ln : lanes) {
-        TCEC_CUDA(cudaSetDevice(ln.device));
-        uint8_t* buf = static_cast<uint8_t*>(ln.ss->packed_a.ptr) + pn.offset;
-        TCEC_NCCL(g_nccl.Broadcast(buf, buf, pn.bytes, ncclUint8, root, ln.comm, ln.ss->s_comm));
-      }
-      if (lanes.size() > 1) TCEC_NCCL(g_nccl.GroupEnd());
+      const int rc = broadcast_panel(lanes, pn, root);
+      if (rc != TCEC_OK) return rc;
       for (Lane& ln : lanes) {
         if (ln.rank == root) continue;
         TCEC_CUDA(cudaSetDevice(ln.device));
@@ -470,13 +487,8 @@ int column_step_host(std::vector<Lane>& lanes, int nranks, int root, int la, int
       if (nranks > 1) TCEC_CUDA(cudaStreamWaitEvent(ln.ss->s_comm, root_bufs->a_free[slot], 0));
     }
     if (nranks > 1 && product) {
-      if (lanes.size() > 1) TCEC_NCCL(g_nccl.GroupStart());
-      for (Lane& ln : lanes) {
-        TCEC_CUDA(cudaSetDevice(ln.device));
-        uint8_t* buf = static_cast<uint8_t*>(ln.ss->packed_a.ptr) + pn.offset;
-        TCEC_NCCL(g_nccl.Broadcast(buf, buf, pn.bytes, ncclUint8, root, ln.comm, ln.ss->s_comm));
-      }
-      if (lanes.size() > 1) TCEC_NCCL(g_nccl.GroupEnd());
+      const int rc = broadcast_panel(lanes, pn, root);
+      if (rc != TCEC_OK) return rc;
     }
     for (size_t i = 0; i < lanes.size(); ++i) {
       Lane& ln = lanes[i];
