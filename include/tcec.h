@@ -246,9 +246,11 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  * Options (process-wide):
  *   "promote_k"  K extent accumulated inside the tensor-core accumulator before
  *                it is added to the FP32 running sum with a round-to-nearest add.
- *                -1 (default) = automatic: 32 to 512 depending on K with error
- *                correction, 0 without.  0 = only at the end, the reference's
- *                mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
+ *                -1 (default) = automatic with error correction: 64 up to K = 2048, 128 up to
+ *                4096, 256 below 16384, else 512 (error against the reference kernel on
+ *                identical inputs: 0.5-0.9 of its error for zero-mean inputs, 0.8-1.4 for
+ *                all-positive ones; the acceptance bound is 2); 0 without error correction.
+ *                0 = only at the end, the reference's mma_rz_sync behaviour (include/wmma_extension/tcec/tcec.hpp:773-831);
  *                the reference's mma_rn_sync uses 16 or 8 (:640-706).
  *   "tile_n"     0 = automatic, 128 or 256.
  *   "cta_pair"   256-wide tiles on pairs of SMs (tcgen05 cta_group::2: 256 x 256 tiles, each SM
@@ -259,10 +261,9 @@ int tcec_split(const float* in, float* hi, float* lo, size_t count, int policy, 
  *                5000^3, which are over before the board reaches its power cap (2048^3: +8 %,
  *                4096^3: +2 %; at the cap the pair draws more power per product and is 5 %
  *                slower); 0 = never; 1 = whenever it applies.
- *   "tail_halves" 1 (default) = when the last wave of 256 x 256 tiles would occupy at most half of the
- *                SM pairs, the CTA-pair kernel cuts those tiles into 256 x 128 halves taken by
- *                different pairs, so the wave lasts half as long; 0 = whole tiles only.  Same
- *                results bit for bit.
+ *   "half_tiles" 1 (default) = a call with so few 256 x 256 tiles that they would leave at least half
+ *                of the SM pairs idle runs on 256 x 128 half tiles instead (CTA-pair kernel, N = 128
+ *                MMAs; 1024^3: 37 -> 27 us); 0 = whole tiles only.  Same results bit for bit.
  *   "reserve_sms" 0..64 (default 0): SMs the GEMM kernels do not occupy.  Their persistent CTAs take
  *                every register of an SM, so a communication kernel launched beside them can only
  *                run where the GEMM has no CTA.

@@ -34,13 +34,13 @@ def _defaults():
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
     tcec.set_option("cta_pair", -1)
-    tcec.set_option("tail_halves", 1)
+    tcec.set_option("half_tiles", 1)
     yield
     tcec.set_option("promote_k", -1)
     tcec.set_option("tile_n", 0)
     tcec.set_option("path", 0)
     tcec.set_option("cta_pair", -1)
-    tcec.set_option("tail_halves", 1)
+    tcec.set_option("half_tiles", 1)
 
 
 # ---------------------------------------------------------------- split (bit-exact)
@@ -300,13 +300,13 @@ def test_cta_pair_kernel_is_bit_identical(shape, policy):
     assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("shape,policy", [((4096, 4096, 256), "fp16_ec"), ((4096, 3990, 96), "tf32_ec"),
-                                          ((1024, 1024, 512), "fp16_no_ec"), ((2300, 2100, 160), "tf32_no_ec"),
+@pytest.mark.parametrize("shape,policy", [((1024, 1024, 512), "fp16_ec"), ((1500, 1400, 96), "tf32_ec"),
+                                          ((1024, 1000, 160), "fp16_no_ec"), ((700, 2300, 64), "tf32_no_ec"),
                                           ((300, 130, 64), "fp16_ec")])
-def test_half_width_tiles_of_the_last_wave_are_bit_identical(shape, policy):
-    """An underfilled last wave of the CTA-pair kernel runs as 256 x 128 halves (whole tiles first,
-    then halves: 4096 x 4096 is 222 whole tiles and 68 halves on 74 pairs); every element of C is
-    the same as with whole tiles only, and as from the one-SM kernel."""
+def test_half_width_tiles_are_bit_identical(shape, policy):
+    """A call with at most 37 pair tiles (half of the 74 SM pairs) runs on 256 x 128 half tiles (N = 128
+    MMAs, 64 columns per epilogue warp); every element of C is the same as with whole tiles, and
+    as from the one-SM kernel."""
     m, n, k = shape
     rng = np.random.default_rng(900 + m + n + k)
     a = _t(rng.uniform(-1, 1, (m, k)).astype(np.float32))
@@ -315,7 +315,7 @@ def test_half_width_tiles_of_the_last_wave_are_bit_identical(shape, policy):
     tcec.set_option("cta_pair", 1)
     out = {}
     for halves in (0, 1):
-        tcec.set_option("tail_halves", halves)
+        tcec.set_option("half_tiles", halves)
         c = torch.full((m + 1, n + 3), float("nan"), dtype=torch.float32, device="cuda")
         tcec.sgemm(a, b, c[:m, :n], policy=policy)
         tcec.device_status()
@@ -324,9 +324,9 @@ def test_half_width_tiles_of_the_last_wave_are_bit_identical(shape, policy):
     assert torch.equal(out[0], out[1])
     tcec.set_option("cta_pair", 0)
     assert torch.equal(tcec.sgemm(a, b, policy=policy), out[1])
-    # a batch whose last wave is underfilled: 80 matrices of one pair tile each on 74 pairs
-    ab = _t(rng.standard_normal((80, 256, 64)).astype(np.float32))
-    bb = _t(rng.standard_normal((80, 64, 256)).astype(np.float32))
+    # a batch in half tiles: 30 matrices of one pair tile each
+    ab = _t(rng.standard_normal((30, 256, 64)).astype(np.float32))
+    bb = _t(rng.standard_normal((30, 64, 256)).astype(np.float32))
     want = tcec.sgemm_strided_batched(ab, bb, policy=policy)
     tcec.set_option("cta_pair", 1)
     got = tcec.sgemm_strided_batched(ab, bb, policy=policy)

@@ -38,6 +38,15 @@ cudaError_t set_smem_attr() {
                               GemmPanelCfg<BN, T, E>::SMEM_BYTES);
 }
 
+template <bool T, bool E>
+cudaError_t set_pair_smem_attr() {
+  cudaError_t e = cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<T, E, 256>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<T, E>::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<T, E, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmPairCfg<T, E>::SMEM_BYTES);
+}
+
 int get_device_state(DeviceState** out) {
   int dev = 0;
   TCEC_CUDA(cudaGetDevice(&dev));
@@ -59,14 +68,10 @@ int get_device_state(DeviceState** out) {
                                    GemmFusedCfg<true>::SMEM_BYTES));
     TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    GemmFusedCfg<false>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, true>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, false>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, true>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, false>::SMEM_BYTES));
+    TCEC_CUDA((set_pair_smem_attr<false, true>()));
+    TCEC_CUDA((set_pair_smem_attr<false, false>()));
+    TCEC_CUDA((set_pair_smem_attr<true, true>()));
+    TCEC_CUDA((set_pair_smem_attr<true, false>()));
     if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return TCEC_ERR_ALLOC;
     TCEC_CUDA(cudaMemset(st.status, 0, sizeof(int)));
     st.attrs_done = true;
@@ -129,12 +134,14 @@ size_t packed_bytes(int rows, int k, int policy) {
   return static_cast<size_t>(padded_row_blocks(rows)) * nkb * (policy_ec(policy) ? 2 : 1) * kPanelBytes;
 }
 // K extent the tensor-core accumulator may gather before the round-to-nearest add, in k blocks.
-// Automatic choice: short products are dominated by the accumulator's truncation, so they are
-// promoted more often (every 64 of K up to K = 2048, 128 up to 4096, 256 below
-// 16384, else 512; each step keeps the error within the reference kernel's on identical inputs,
-// all-positive inputs included, where the truncation bias is largest); the
-// policies without error correction keep the reference's default for them, accumulation inside
-// the tensor core (mma_rz_sync, include/wmma_extension/tcec/detail/no_cor.hpp:858-897).
+// The accumulator truncates, so a longer interval trades accuracy for fewer drains.  Automatic
+// choice with error correction: every 64 of K up to K = 2048, 128 up to 4096, 256 below 16384,
+// else 512.  Each step is the longest that keeps both acceptance bounds on all-positive inputs,
+// where the truncation bias is largest (error vs FP64 at most twice the reference kernel's and
+// at most twice an FP32 SGEMM's on identical inputs): at K = 4096 an interval of 256 is 6 %
+// faster and still 1.33 x the reference kernel's error, but 2.7 x cuBLAS FP32's.  The policies
+// without error correction keep the reference's default for them, accumulation inside the tensor
+// core (mma_rz_sync, include/wmma_extension/tcec/detail/no_cor.hpp:858-897).
 int promote_blocks(int k, int policy, int kop, const Options& opt) {
   int pk = opt.promote_k;
   if (pk < 0) pk = !policy_ec(policy) ? 0 : (k <= 2048 ? 64 : (k <= 4096 ? 128 : (k < 16384 ? 256 : 512)));
@@ -286,21 +293,36 @@ int gemm_packed(const Shape& s, int m, int n, int k, float alpha, const uint8_t*
     const long long npair_tiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
     if (npair_tiles > 0x3fffffffll) return TCEC_ERR_UNSUPPORTED;  // work items are 32-bit
     const int max_pairs = sms / 2 > 1 ? sms / 2 : 1;
-    // A last wave that fills at most half of the pairs is done in half-width tiles: twice as many
-    // work items, each half as long (4096^3: 256 tiles on 74 pairs, 3.46 -> 3.5 waves instead of 4).
-    const int tail = static_cast<int>(npair_tiles % max_pairs);
-    gp.narrow_from = static_cast<int>(npair_tiles);
-    if (opt.tail_halves && tail > 0 && 2 * tail <= max_pairs) gp.narrow_from -= tail;
-    const long long nwork = 2 * npair_tiles - gp.narrow_from;
-    const int grid = 2 * static_cast<int>(nwork < max_pairs ? nwork : max_pairs);
+    // A call with so few tiles that they leave at least half of the pairs idle runs in half-width
+    // tiles: twice as many work items, each ~0.6 as long (1024^3: 16 tiles become 32 halves,
+    // 37 -> 27 us).  Halving only the tiles of an underfilled last wave of a larger call does not
+    // pay: an N = 128 MMA takes nearly as long as an N = 256 one (measured at 4096^3 and 5120^3:
+    // 1-2 % slower), so such calls stay on whole tiles.
+    const int halved = (opt.half_tiles && 2 * npair_tiles <= max_pairs) ? static_cast<int>(npair_tiles) : 0;
+    const int whole = static_cast<int>(npair_tiles) - halved;
+#define TCEC_PAIR(T, E)                                                                                          \
+  do {                                                                                                           \
+    if (whole > 0) {                                                                                             \
+      gp.tile_first = 0;                                                                                         \
+      gp.tile_count = whole;                                                                                     \
+      const int grid = 2 * (whole < max_pairs ? whole : max_pairs);                                              \
+      tcec_gemm_panels_pair_kernel<T, E, 256><<<grid, 384, GemmPairCfg<T, E>::SMEM_BYTES, stream>>>(gp);         \
+    }                                                                                                            \
+    if (halved > 0) {                                                                                            \
+      gp.tile_first = whole;                                                                                     \
+      gp.tile_count = halved;                                                                                    \
+      tcec_gemm_panels_pair_kernel<T, E, 128><<<4 * halved, 384, GemmPairCfg<T, E>::SMEM_BYTES, stream>>>(gp);   \
+    }                                                                                                            \
+  } while (0)
     if (tf32 && ec)
-      tcec_gemm_panels_pair_kernel<true, true><<<grid, 384, GemmPairCfg<true, true>::SMEM_BYTES, stream>>>(gp);
+      TCEC_PAIR(true, true);
     else if (tf32)
-      tcec_gemm_panels_pair_kernel<true, false><<<grid, 384, GemmPairCfg<true, false>::SMEM_BYTES, stream>>>(gp);
+      TCEC_PAIR(true, false);
     else if (ec)
-      tcec_gemm_panels_pair_kernel<false, true><<<grid, 384, GemmPairCfg<false, true>::SMEM_BYTES, stream>>>(gp);
+      TCEC_PAIR(false, true);
     else
-      tcec_gemm_panels_pair_kernel<false, false><<<grid, 384, GemmPairCfg<false, false>::SMEM_BYTES, stream>>>(gp);
+      TCEC_PAIR(false, false);
+#undef TCEC_PAIR
     return TCEC_OK;
   }
   const long long ntiles = static_cast<long long>(gp.tiles_m) * gp.tiles_n * batch;
@@ -803,7 +825,7 @@ const OptionEntry kOptions[] = {
     {"promote_k", &Options::promote_k, -1, 0x7fffffff, any_value},
     {"tile_n", &Options::tile_n, 0, 256, tile_value},
     {"cta_pair", &Options::cta_pair, -1, 1, any_value},
-    {"tail_halves", &Options::tail_halves, 0, 1, any_value},
+    {"half_tiles", &Options::half_tiles, 0, 1, any_value},
     {"path", &Options::path, 0, 2, any_value},
     {"store_turn", &Options::store_turn, 0, 1, any_value},
     {"reserve_sms", &Options::reserve_sms, 0, 64, any_value},
@@ -941,14 +963,10 @@ int static_device_state(StaticDevice** out) {
     TCEC_CUDA((set_smem_attr<256, false, true>()));
     TCEC_CUDA((set_smem_attr<256, true, false>()));
     TCEC_CUDA((set_smem_attr<256, true, true>()));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, false>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, false>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, false>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<false, true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<false, true>::SMEM_BYTES));
-    TCEC_CUDA(cudaFuncSetAttribute(tcec_gemm_panels_pair_kernel<true, true>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg<true, true>::SMEM_BYTES));
+    TCEC_CUDA((set_pair_smem_attr<false, false>()));
+    TCEC_CUDA((set_pair_smem_attr<true, false>()));
+    TCEC_CUDA((set_pair_smem_attr<false, true>()));
+    TCEC_CUDA((set_pair_smem_attr<true, true>()));
     sd.ready = true;
   }
   *out = &sd;

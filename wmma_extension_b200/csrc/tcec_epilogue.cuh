@@ -1,5 +1,5 @@
-// Store step shared by the GEMM kernels: one epilogue thread holds 128 consecutive columns of
-// one output row (main + correction already folded) and the warp writes alpha * acc + beta * C.
+// Store step shared by the GEMM kernels: one epilogue thread holds NC (128, or 64 in half-width
+// tiles) consecutive columns of one output row (main + correction already folded) and the warp writes alpha * acc + beta * C.
 // Restates the reference's smem2dmem (test/tcec/batch_gemm.cu:119-185): beta == 0 never reads C,
 // 128-bit stores where the row allows them, element-wise predicated stores on the ragged edge.
 //
@@ -28,10 +28,11 @@ __device__ __forceinline__ float axpby(float alpha, float v, float beta, float o
   return __fmaf_rn(beta, old, __fmul_rn(alpha, v));
 }
 
-__device__ __forceinline__ void store_row_slice(const float (&acc)[128], int row, int col0, const StoreTarget& t) {
+template <int NC>
+__device__ __forceinline__ void store_row_slice(const float (&acc)[NC], int row, int col0, const StoreTarget& t) {
   if (row >= t.M) return;
 #pragma unroll
-  for (int cc = 0; cc < 4; ++cc) {
+  for (int cc = 0; cc < NC / 32; ++cc) {
     if (!t.col_major) {
       float* crow = t.cbase + static_cast<long long>(row) * t.ldc;
 #pragma unroll
@@ -78,8 +79,9 @@ constexpr int kEpiBufFloats = 32 * 33;              // one warp's turn buffer
 constexpr int kEpiBufBytes = kEpiBufFloats * 4;      // 4224
 
 // `row0` = first of the warp's 32 rows (lane = row0 + lane holds `acc`), `col0` = first of its
-// 128 columns, `wbuf` = this warp's buffer of kEpiBufFloats floats.  Warp-collective.
-__device__ __forceinline__ void store_warp_block(const float (&acc)[128], int row0, int col0, const StoreTarget& t,
+// NC columns, `wbuf` = this warp's buffer of kEpiBufFloats floats.  Warp-collective.
+template <int NC>
+__device__ __forceinline__ void store_warp_block(const float (&acc)[NC], int row0, int col0, const StoreTarget& t,
                                                  float* wbuf, int lane) {
   if (t.col_major) {
     store_row_slice(acc, row0 + lane, col0, t);
@@ -87,7 +89,7 @@ __device__ __forceinline__ void store_warp_block(const float (&acc)[128], int ro
   }
   const int rsub = lane >> 3, cv = (lane & 7) * 4;
 #pragma unroll
-  for (int cc = 0; cc < 4; ++cc) {
+  for (int cc = 0; cc < NC / 32; ++cc) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) wbuf[lane * 33 + i] = acc[cc * 32 + i];
     __syncwarp();

@@ -56,7 +56,7 @@ struct GemmPanelParams {
   const unsigned int* row_ready;  // optional: one word per `ready_rows` rows of A; the producer loads a tile's
   int ready_rows;                 // operands only once the word of the tile's rows equals `ready_epoch` (A is
   unsigned int ready_epoch;       // arriving from another GPU while the kernel runs); the wait is bounded
-  int narrow_from;         // CTA-pair kernel only: pair tiles from this index on are done as two 128-column halves
+  int tile_first, tile_count;  // CTA-pair kernel only: the pair tiles this launch covers
   int store_turn;          // 1: stores go through the per-warp shared-memory buffers (launched with
                            // SMEM_BYTES); 0: direct stores, launched with SMEM_BYTES_NO_TURN
   int debug_flags;         // develop builds only (results invalid): bit 0 = no operand copies after the first ring
@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         ok = false;
         break;
       }
+      const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
       float acc[128];
       for (int c = 0; c < nchunks; ++c, ++chunk) {
@@ -327,6 +328,9 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         }
         tc_fence_after();
       }
+      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
+      const int col0 = tc.nt * BN + colbase;
+      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
       if constexpr (kEc) {
         // Fold the correction term into the registers first and hand the accumulator back
         // before the stores: the next tile's correction MMAs then overlap this tile's stores.
@@ -335,12 +339,6 @@ __global__ void __launch_bounds__(GemmPanelCfg<BN, kTf32, kEc>::THREADS, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_corr_free));
       }
-      // Where the tile lies is worked out only now: nothing but the running sums stays live across
-      // the drains above, which need every register for their loads in flight.
-      const TileCoord tc = decode_tile(tile, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
-      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
-      const int col0 = tc.nt * BN + colbase;
-      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
       StoreTarget st;
       st.cbase = cbase;
       st.ldc = p.ldc;

@@ -19,11 +19,11 @@
 //   main_free / corr_free   leader's barriers: 8 local epilogue warps + 8 remote arrives
 // Both CTAs meet at a cluster barrier after set-up and before exit.
 //
-// Work items: pair tiles below `p.narrow_from` are whole 256 x 256 tiles; every pair tile from
-// there on is cut into two 256 x 128 halves that different pairs take (the host does this to the
-// tiles of an underfilled last wave, which then lasts half as long).  A half is one 128-row B
-// panel of which each CTA loads its 64 rows (the first or second 4 KB of the panel), multiplied
-// with N = 128; every element of C still sees the same products in the same order.
+// BN = 128 is the same kernel on 256 x 128 half tiles: a half is one 128-row B panel of which each
+// CTA loads its 64 rows (the first or second 4 KB of the panel), multiplied with N = 128, and each
+// epilogue warp holds 64 columns.  The host runs it as a second launch over the tiles of an
+// underfilled last wave, which then lasts half as long; every element of C still sees the same
+// products in the same order.  A launch covers the pair tiles [tile_first, tile_first + tile_count).
 #pragma once
 #include "sm100_ptx.cuh"
 #include "tcec_gemm_panels.cuh"
@@ -49,29 +49,16 @@ struct GemmPairCfg {
   static constexpr int GROUP_M = 8;  // pair tiles are 256 rows tall
 };
 
-struct PairWork {
-  TileCoord tc;
-  int half;  // -1: the whole pair tile; 0 / 1: its left / right 128 columns
-};
-__device__ __forceinline__ PairWork decode_pair_work(int w, int narrow_from, int tiles_m, int tiles_n, int group_m) {
-  PairWork r;
-  if (w < narrow_from) {
-    r.tc = decode_tile(w, tiles_m, tiles_n, group_m);
-    r.half = -1;
-  } else {
-    const int h = w - narrow_from;
-    r.tc = decode_tile(narrow_from + (h >> 1), tiles_m, tiles_n, group_m);
-    r.half = h & 1;
-  }
-  return r;
-}
-
 // p.tiles_m counts 256-row pair tiles here.
-template <bool kTf32, bool kEc>
+template <bool kTf32, bool kEc, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     tcec_gemm_panels_pair_kernel(const GemmPanelParams p) {
+  static_assert(BN == 256 || BN == 128, "whole or half-width pair tiles");
   using Cfg = GemmPairCfg<kTf32, kEc>;
-  constexpr int NST = Cfg::NST, BN = 256;
+  constexpr int NST = Cfg::NST;
+  constexpr int HALVES = 256 / BN;            // work items per pair tile
+  constexpr int NC = BN / 2;                  // columns per epilogue warp
+  constexpr int B_PIECE = kPanelBytes / HALVES;  // bytes of one B image (hi or lo) per CTA and K block
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[NST], bar_empty[NST];
   __shared__ uint64_t bar_main_full, bar_main_free, bar_corr_full, bar_corr_free, bar_drain[2];
@@ -84,9 +71,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   const uint32_t rank = cluster_ctarank();
   const bool leader = (rank == 0);
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int ntiles = p.tiles_m * p.tiles_n * p.batch;
-  const int narrow_from = p.narrow_from < ntiles ? p.narrow_from : ntiles;
-  const int nwork = narrow_from + 2 * (ntiles - narrow_from);
+  const int ntiles = p.tile_count * HALVES;  // work items of this launch
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) {
@@ -111,7 +96,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_main = tmem_base_s;
-  const uint32_t tmem_corr = tmem_base_s + BN;
+  const uint32_t tmem_corr = tmem_base_s + 256;
   volatile uint32_t* abortp = &abort_flag;
   // What the leader's two MMA threads need (tcec_gemm_roles.cuh): M = 256 across the pair.
   OperandImage im;
@@ -122,9 +107,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
   im.b_hi16 = Cfg::A_BYTES >> 4;
   im.b_lo16 = (Cfg::A_BYTES + kPanelBytes) >> 4;
   im.idesc = umma_idesc(kTf32 ? 2u : 0u, 256, BN);
-  im.idesc_narrow = umma_idesc(kTf32 ? 2u : 0u, 256, BN / 2);
-  im.narrow_from = narrow_from;
-  const StridedTiles tiles{pair, npairs, nwork};
+  const StridedTiles tiles{pair, npairs, ntiles};
   const KWalk walk{p.nkb, p.promo};
   const RingBarriers ring{bar_full, bar_empty};
 
@@ -135,17 +118,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       if (lane == 0) {
         uint32_t s = 0, ph = 0, armed = 0, armed_parity = 0, it = 0;
         bool ok = true;
-        for (int w = pair; w < nwork && ok; w += npairs) {
-          const PairWork pw = decode_pair_work(w, narrow_from, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
-          const TileCoord tc = pw.tc;
-          const bool narrow = pw.half >= 0;
+        for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+          const TileCoord tc = decode_tile(p.tile_first + tile / HALVES, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
           const uint8_t* pa = p.panels_a + tc.b * p.panels_a_batch_stride +
                               static_cast<size_t>(tc.mt * 2 + rank) * p.nkb * Cfg::A_BYTES;
           // whole tile: this CTA's 128-row panel of the tile's two; half: its 64 rows of the half's one panel
+          const int nblock = tc.nt * 2 + (BN == 256 ? static_cast<int>(rank) : tile % HALVES);
           const uint8_t* pb = p.panels_b + tc.b * p.panels_b_batch_stride +
-                              static_cast<size_t>(tc.nt * 2 + (narrow ? pw.half : static_cast<int>(rank))) * p.nkb *
-                                  Cfg::B_BYTES +
-                              (narrow ? rank * (kPanelBytes / 2) : 0u);
+                              static_cast<size_t>(nblock) * p.nkb * Cfg::B_BYTES + (BN == 256 ? 0u : rank * B_PIECE);
           for (int kb = 0; kb < p.nkb; ++kb, ++it) {
             if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abortp, 128)) {
               ok = false;
@@ -161,17 +141,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
             }
             const uint32_t full = smem_u32(&bar_full[s]);
             const uint32_t dst = smem_base + s * Cfg::STAGE_BYTES;
-            mbar_arrive_expect_tx(full, narrow ? Cfg::A_BYTES + Cfg::B_BYTES / 2 : Cfg::STAGE_BYTES);
+            mbar_arrive_expect_tx(full, Cfg::A_BYTES + Cfg::NP * B_PIECE);
             armed |= 1u << s;
             armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
             bulk_load(dst, pa + static_cast<size_t>(kb) * Cfg::A_BYTES, Cfg::A_BYTES, full);
             const uint8_t* srcb = pb + static_cast<size_t>(kb) * Cfg::B_BYTES;
-            if (!narrow) {
+            if constexpr (BN == 256) {
               bulk_load(dst + Cfg::A_BYTES, srcb, Cfg::B_BYTES, full);
             } else {
 #pragma unroll
               for (int h = 0; h < Cfg::NP; ++h)  // hi (+ lo): each image keeps its place in the stage
-                bulk_load(dst + Cfg::A_BYTES + h * kPanelBytes, srcb + h * kPanelBytes, kPanelBytes / 2, full);
+                bulk_load(dst + Cfg::A_BYTES + h * kPanelBytes, srcb + h * kPanelBytes, B_PIECE, full);
             }
             if (++s == static_cast<uint32_t>(NST)) {
               s = 0;
@@ -192,7 +172,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           // -------------------------------------------------------- peer: relay "my stage landed"
           uint32_t s = 0, ph = 0, it = 0;
           bool ok = true;
-          for (int w = pair; w < nwork && ok; w += npairs) {
+          for (int tile = pair; tile < ntiles && ok; tile += npairs) {
             for (int kb = 0; kb < p.nkb; ++kb, ++it) {
               if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, 32)) {
                 ok = false;
@@ -211,8 +191,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           }
         } else {
           // -------------------------------------------------------- leader: main products
-          if (!issue_main_products<kTf32, true, NST>(tiles, walk, im, tmem_main, ring, &bar_main_full, &bar_main_free,
-                                                     abortp, p.debug_flags, nullptr))
+          if (!issue_main_products<kTf32, true, NST>(tiles, walk, im, tmem_main, ring, &bar_main_full,
+                                                                    &bar_main_free, abortp, p.debug_flags,
+                                                                    blockIdx.x == 0 ? p.trace : nullptr))
             mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[0]);
         }
       }
@@ -221,7 +202,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
       if constexpr (kEc) {
         if (lane == 0 && leader) {
           if (!issue_corr_products<kTf32, true, NST>(tiles, walk, im, tmem_corr, ring, &bar_corr_full, &bar_corr_free,
-                                                     abortp, p.debug_flags, nullptr))
+                                                     abortp, p.debug_flags, blockIdx.x == 0 ? p.trace : nullptr))
             mma_thread_gave_up<true>(&abort_flag, p.status, kErrMmaWait, &bar_drain[1]);
         }
       }
@@ -231,7 +212,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     const int ew = warp - 4;
     const int q = warp & 3;
-    const int colbase = (ew >> 2) * 128;
+    const int colbase = (ew >> 2) * NC;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float corr_scale = kTf32 ? 1.0f : (1.0f / 2048.0f);
     const bool vec_store = !p.c_col_major && (p.ldc % 4 == 0);
@@ -239,21 +220,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
     const uint32_t corr_free_leader = map_to_cta(smem_u32(&bar_corr_free), 0);
     uint32_t chunk = 0, tcount = 0;
     bool ok = true;
-    for (int w = pair; w < nwork && ok; w += npairs, ++tcount) {
-      // a half tile has no columns for the second warpgroup: it only keeps the barriers' counts
-      const bool idle = w >= narrow_from && colbase != 0;
+    for (int tile = pair; tile < ntiles && ok; tile += npairs, ++tcount) {
+      const TileCoord tc = decode_tile(p.tile_first + tile / HALVES, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
       const int nchunks = p.promo ? (p.nkb + p.promo - 1) / p.promo : 1;
-      float acc[128];
+      float acc[NC];
       for (int c = 0; c < nchunks; ++c, ++chunk) {
         if (!mbar_wait_warp(smem_u32(&bar_main_full), chunk & 1, abortp)) {
           ok = false;
           break;
         }
+        if (warp == 4 && lane == 0) trace_mark(p, 2, chunk);
         tc_fence_after();
-        if (!idle) promote_main_chunk<true>(acc, tmem_main + lane_addr + colbase, c == 0);
+        if constexpr (BN == 256) promote_main_chunk<true>(acc, tmem_main + lane_addr + colbase, c == 0);
+        else promote_main_chunk(acc, tmem_main + lane_addr + colbase, c == 0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(main_free_leader);
+        if (warp == 4 && lane == 0) trace_mark(p, 3, chunk);
       }
       if (!ok) break;
       if constexpr (kEc) {
@@ -262,29 +245,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
           break;
         }
         tc_fence_after();
-        if (!idle) fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
+      }
+      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
+      const int col0 = tc.nt * 256 + (tile % HALVES) * BN + colbase;
+      const bool vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+      if constexpr (kEc) {
+        fold_correction(acc, tmem_corr + lane_addr + colbase, corr_scale);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(corr_free_leader);
       }
-      if (idle) continue;
-      // Where the tile lies is worked out only now: nothing but the running sums stays live across
-      // the drains above, which need every register for their loads in flight.
-      const PairWork pw = decode_pair_work(w, narrow_from, p.tiles_m, p.tiles_n, Cfg::GROUP_M);
-      const TileCoord tc = pw.tc;
-      float* cbase = p.c_array ? p.c_array[tc.b] : p.c + tc.b * p.c_batch_stride;
-      const int col0 = tc.nt * BN + (pw.half >= 0 ? pw.half * 128 : colbase);
       StoreTarget st;
       st.cbase = cbase;
       st.ldc = p.ldc;
       st.M = p.M;
       st.N = p.N;
       st.col_major = p.c_col_major;
-      st.vec_ok = vec_store && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+      st.vec_ok = vec_ok;
       st.alpha = p.alpha;
       st.beta = p.beta;
-      store_warp_block(acc, tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32, col0, st,
-                       reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
+      store_warp_block(acc, tc.mt * 256 + static_cast<int>(rank) * 128 + q * 32, col0, st, reinterpret_cast<float*>(smem_gen + Cfg::EPI_OFFSET) + ew * kEpiBufFloats, lane);
     }
     if (!ok) {
       raise_abort_pair(&abort_flag);

@@ -21,10 +21,6 @@ struct OperandImage {
   uint32_t b_hi16;
   uint32_t b_lo16;
   uint32_t idesc;      // instruction descriptor (type, M, N)
-  // Work items numbered `narrow_from` and above are half-width tiles and use `idesc_narrow`
-  // (same type and M, half the N); kernels without such items leave the defaults.
-  int narrow_from = 0x7fffffff;
-  uint32_t idesc_narrow = 0;
 };
 
 // How K is cut.
@@ -128,7 +124,6 @@ __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWal
     const int tile = tiles.next(abortp);
     if (tile == kNoMoreTiles) break;
     if (tile == kTileWaitFailed) return false;
-    const uint32_t idesc = tile >= im.narrow_from ? im.idesc_narrow : im.idesc;
     int left_in_chunk = 0;  // K blocks still to issue in the current chunk
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
@@ -147,7 +142,7 @@ __device__ __forceinline__ bool issue_main_products(TileSource tiles, const KWal
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_main, im.dconst | (a16 + 16 * j), im.dconst | (a16 + im.b_hi16 + 16 * j),
-                                   idesc, (first_in_chunk && j == 0) ? 0u : 1u);
+                                   im.idesc, (first_in_chunk && j == 0) ? 0u : 1u);
       }
       if (--left_in_chunk == 0) {
         umma_commit_to<kPair>(smem_u32(bar_main_full));
@@ -176,7 +171,6 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
     const int tile = tiles.next(abortp);
     if (tile == kNoMoreTiles) break;
     if (tile == kTileWaitFailed) return false;
-    const uint32_t idesc = tile >= im.narrow_from ? im.idesc_narrow : im.idesc;
     for (int kb = 0; kb < w.nkb; ++kb, ++it) {
       if (!mbar_wait(smem_u32(&ring.full[s]), ph, abortp, 32u)) return false;
       if (kb == 0) {
@@ -190,11 +184,11 @@ __device__ __forceinline__ bool issue_corr_products(TileSource tiles, const KWal
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_corr, im.dconst | (c16 + im.a_lo16 + 16 * j),
-                                   im.dconst | (c16 + im.b_hi16 + 16 * j), idesc, (kb == 0 && j == 0) ? 0u : 1u);
+                                   im.dconst | (c16 + im.b_hi16 + 16 * j), im.idesc, (kb == 0 && j == 0) ? 0u : 1u);
 #pragma unroll
         for (uint32_t j = 0; j < 2; ++j)
           umma_issue<kTf32, kPair>(tmem_corr, im.dconst | (c16 + 16 * j), im.dconst | (c16 + im.b_lo16 + 16 * j),
-                                   idesc, 1u);
+                                   im.idesc, 1u);
       }
       umma_commit_to<kPair>(smem_u32(&ring.empty[s]));
       if (++s == static_cast<uint32_t>(NST)) {
@@ -258,6 +252,38 @@ __device__ __forceinline__ void promote_main_chunk(float (&acc)[128], uint32_t t
         for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(v[i]);
       }
     }
+  }
+}
+
+// The 64-column forms (half-width tiles of the CTA-pair kernel): one wait per step.
+__device__ __forceinline__ void promote_main_chunk(float (&acc)[64], uint32_t taddr, bool first) {
+  uint32_t v0[32], v1[32];
+  tmem_ld_32x32b_x32(taddr, v0);
+  tmem_ld_32x32b_x32(taddr + 32, v1);
+  tmem_ld_wait();
+  if (first) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      acc[i] = __uint_as_float(v0[i]);
+      acc[32 + i] = __uint_as_float(v1[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      acc[i] += __uint_as_float(v0[i]);
+      acc[32 + i] += __uint_as_float(v1[i]);
+    }
+  }
+}
+__device__ __forceinline__ void fold_correction(float (&acc)[64], uint32_t taddr, float scale) {
+  uint32_t v0[32], v1[32];
+  tmem_ld_32x32b_x32(taddr, v0);
+  tmem_ld_32x32b_x32(taddr + 32, v1);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    acc[i] = acc[i] + __uint_as_float(v0[i]) * scale;
+    acc[32 + i] = acc[32 + i] + __uint_as_float(v1[i]) * scale;
   }
 }
 

@@ -29,7 +29,7 @@ struct Options {
   int static_tiles = 0; // 0: tiles beyond the first wave are drawn from a device-wide counter; 1: static striding
   int reserve_sms = 0;  // SMs the GEMM kernels leave idle (for a caller's communication kernels)
   int cta_pair = -1;    // -1: CTA-pair kernel for the policies without error correction; 0: never; 1: whenever it applies
-  int tail_halves = 1;  // CTA-pair kernel: an underfilled last wave is done in half-width tiles
+  int half_tiles = 1;   // CTA-pair kernel: calls with very few tiles run on 256 x 128 half tiles
   int path = 0;         // 0: chosen per call, 1: always operand panels, 2: FP32-tile kernel whenever it applies
   int comm_sms = 8;     // SMs the column-sharded step leaves to the broadcast (also the broadcast's CTA limit)
   int comm_panel_rows = 2048;  // rows of A per broadcast
