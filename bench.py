@@ -474,7 +474,7 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
     torch.cuda.synchronize()
 
     def e2e_step():
-        tcec.sgemm_host(ah, bh, ch, policy=policy, panel_rows=args.panel_rows)
+        tcec.sgemm_host(ah, bh, ch, policy=policy)  # automatic panel height
 
     e2e_step()
     tcec.sgemm(a, b, c, policy=policy)

@@ -132,7 +132,7 @@ int tcec_static_status(int* detail);
 
 /*
  * tcec_sgemm on HOST operands (pinned memory makes the copies asynchronous): B is copied in and
- * split once, A travels in panels of `panel_rows` rows (0 = 2048), and the copy-in of panel p+1,
+ * split once, A travels in panels of `panel_rows` rows (0 = automatic: 512), and the copy-in of panel p+1,
  * the GEMM on panel p and the copy-out of panel p-1 overlap on three streams.  The call returns
  * once everything is queued; the result is complete when `stream` has reached the end of the
  * call's work (synchronise it, or record an event on it, before reading c_host).  The reference

@@ -386,7 +386,7 @@ def _require_host_f32(*ts: torch.Tensor) -> None:
 
 
 def sgemm_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, *, alpha: float = 1.0,
-               beta: float = 0.0, policy="fp16_ec", panel_rows: int = 2048,
+               beta: float = 0.0, policy="fp16_ec", panel_rows: int = 0,
                device: Optional[torch.device] = None) -> torch.Tensor:
     """C = alpha * A @ B + beta * C for operands in (pinned) HOST memory, through ``tcec_sgemm_host``.
 
