@@ -273,6 +273,32 @@ def time_loop(torch, fn, steps, dist_on):
     return e0.elapsed_time(e1)
 
 
+def per_step_times(torch, fn, steps):
+    """Device time of each of `steps` calls (an event pair per call); for best / median beside the loop's mean."""
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for e0, e1 in ev:
+        e0.record()
+        fn()
+        e1.record()
+    torch.cuda.synchronize()
+    return sorted(e0.elapsed_time(e1) for e0, e1 in ev)
+
+
+def error_metrics(torch, c, exact):
+    """The three error forms of the reference's tests against an FP64 product of the whole matrix: max |d| / max |ref|
+    (test/primitive/common.hpp:100-102), relative Frobenius residual (test/tcec/batch_gemm.cu:605), max |d|
+    (test/tcec/mma.cu:152).  Non-finite elements of c (fp16 heads that overflowed) are left out and counted."""
+    finite = torch.isfinite(c)
+    d = torch.where(finite, c.double() - exact, torch.zeros_like(exact))
+    out = {"max_rel": (d.abs().max() / exact.abs().max()).item(),
+           "fro_rel": (torch.linalg.norm(d) / torch.linalg.norm(exact)).item(), "max_abs": d.abs().max().item()}
+    nf = 1.0 - finite.double().mean().item()
+    if nf:
+        out["nonfinite_fraction"] = nf
+    return out
+
+
 def max_over_ranks(torch, value, device, dist_on):
     if not dist_on:
         return value
@@ -369,6 +395,20 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
     size = args.size
     m = n = k = size
     policy = args.policy if args.only == "kernel" else "fp16_ec"
+    tf32_peak = None
+    if args.only != "kernel":
+        # ---- measured dense tf32 throughput of the box (cuBLAS through torch), for the tf32 policy's roofline: a burst
+        #      figure like the 16-bit one of MEASURED_PEAKS.json, so it is taken first, before the long loops heat the GPU
+        x = torch.randn((8192, 8192), device=device)
+        y = torch.randn((8192, 8192), device=device)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        for _ in range(3):
+            torch.matmul(x, y)
+        best = min(time_loop(torch, lambda: torch.matmul(x, y), 1, False) for _ in range(10))
+        torch.backends.cuda.matmul.allow_tf32 = prev
+        tf32_peak = 2.0 * 8192 ** 3 / (best * 1e-3) * 1e-12
+        del x, y
     a = make_uniform(torch, device, m, k, seed=3)
     b = make_uniform(torch, device, k, n, seed=1003)
     c = torch.empty((m, n), dtype=torch.float32, device=device)
@@ -403,11 +443,22 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
         print(json.dumps(line), flush=True)
         return
 
-    # ---- dominant kernel alone (operands already split), for the roofline
+    # ---- the dominant kernel inside the step, for the roofline: the step's own three launches (split A,
+    #      split B, GEMM: tcec_pack_a / tcec_pack_b / tcec_sgemm_packed issue exactly what tcec_sgemm does), back
+    #      to back as in the timed region, with an event pair around each GEMM launch
     ap, bp = tcec.pack_a(a, policy), tcec.pack_b(b, policy)
-    for _ in range(3):
+    for _ in range(2):
         tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy)
-    ms_k = time_loop(torch, lambda: tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy), args.steps, False)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for e0, e1 in kev:
+        tcec.pack_a(a, policy, out=ap)
+        tcec.pack_b(b, policy, out=bp)
+        e0.record()
+        tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy)
+        e1.record()
+    torch.cuda.synchronize()
+    ms_k = sum(e0.elapsed_time(e1) for e0, e1 in kev)
     achieved = flop / (ms_k / args.steps * 1e-3) * 1e-12
     del ap, bp
     peak = peaks["bf16_burst"] / 3.0
@@ -420,7 +471,8 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
         "frac_of_sustained_peak": achieved / (peaks["bf16_sustained"] / 3.0),
         "sustained_is": "the same with the sustained dense figure: this kernel runs ~20 ms per launch, back to back, at "
                         "the board's power cap",
-        "kernel": "tcec_gemm_panels_kernel<256,fp16,ec>", "kernel_ms": ms_k / args.steps}
+        "kernel": "tcec_gemm_panels_kernel<256,fp16,ec>", "kernel_ms": ms_k / args.steps,
+        "kernel_timed": "an event pair around each GEMM launch of full steps (split A, split B, GEMM) run back to back"}
 
     # ---- accuracy of the headline on sampled rows (outside any timed region)
     rows = [0, 1, m // 2 - 1, m // 2, m - 1]
@@ -433,18 +485,18 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
     e_h, nf_h, e_f = errors_of(a, b, policy)
     line["accuracy"] = {"rows_checked": len(rows), "max_rel": e_h, "fp16_ec_max_rel": e_h, "fp32_fma_max_rel": e_f,
                         "nonfinite_fraction": nf_h}
-
-    # ---- measured dense tf32 throughput of the box (cuBLAS through torch), for the tf32 policy's roofline
-    x = torch.randn((8192, 8192), device=device)
-    y = torch.randn((8192, 8192), device=device)
+    # the whole matrix against a GPU FP64 product, for this library and for cuBLAS FP32 on the same inputs
+    exact = a.double() @ b.double()
+    line["accuracy"]["full_matrix_vs_gpu_fp64"] = {policy: error_metrics(torch, c, exact)}
     prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = True
-    for _ in range(3):
-        torch.matmul(x, y)
-    best = min(time_loop(torch, lambda: torch.matmul(x, y), 1, False) for _ in range(10))
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.matmul(a, b, out=c)
     torch.backends.cuda.matmul.allow_tf32 = prev
-    tf32_peak = 2.0 * 8192 ** 3 / (best * 1e-3) * 1e-12
-    del x, y
+    line["accuracy"]["full_matrix_vs_gpu_fp64"]["cublas_fp32"] = error_metrics(torch, c, exact)
+    del exact
+    # best and median of single calls, beside the mean of the timed loop
+    t = per_step_times(torch, step, max(10, args.steps))
+    line["ms_per_step_best"], line["ms_per_step_median"] = t[0], t[len(t) // 2]
 
     # ---- same shape, wide-exponent values: tf32 policy (accurate) vs fp16 policy (heads overflow)
     aw, bw = make_wide(torch, device, m, k, seed=3), make_wide(torch, device, k, n, seed=1003)
@@ -457,6 +509,9 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
         e, nf, e32 = errors_of(aw, bw, pol)
         wide[pol] = {"tflops": flop / (ms_t / st * 1e-3) * 1e-12, "max_rel_err_finite": e, "nonfinite_fraction": nf}
         wide["fp32_fma_max_rel"] = e32
+        exact = aw.double() @ bw.double()
+        wide[pol]["full_matrix_vs_gpu_fp64"] = error_metrics(torch, c, exact)  # c still holds errors_of's product
+        del exact
     wide["tf32_dense_peak_measured"] = tf32_peak
     wide["tf32_ec"]["frac_of_tf32_roofline"] = wide["tf32_ec"]["tflops"] / (tf32_peak / 3.0)
     wide["tf32_roofline_is"] = "dense tf32 throughput measured in this run (torch.matmul with TF32 allowed, 8192^3, best " \
@@ -498,17 +553,22 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
         tcec.sgemm(a2, b2, c2, policy=policy)
     reps = max(10, args.steps)
     ms2 = time_loop(torch, lambda: tcec.sgemm(a2, b2, c2, policy=policy), reps, False) / reps
+    t2 = per_step_times(torch, lambda: tcec.sgemm(a2, b2, c2, policy=policy), reps)
     exact = a2.double() @ b2.double()
     scale = exact.abs().max()
-    err2 = ((c2.double() - exact).abs().max() / scale).item()
+    m_ours = error_metrics(torch, c2, exact)
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
-    err2_f32 = (((a2 @ b2).double() - exact).abs().max() / scale).item()
+    m_f32 = error_metrics(torch, a2 @ b2, exact)
     torch.backends.cuda.matmul.allow_tf32 = prev
     line["square_4096"] = {"workload": "sgemm M=N=K=4096, FP32 row-major, U[-1,1), fp16_ec (both splits + GEMM per call)",
                            "tflops": 2.0 * s2 ** 3 / (ms2 * 1e-3) * 1e-12, "ms_per_call": ms2,
+                           "ms_best": t2[0], "ms_median": t2[len(t2) // 2],
                            "frac_of_roofline": 2.0 * s2 ** 3 / (ms2 * 1e-3) * 1e-12 / peak,
-                           "max_rel_err_full_matrix": err2, "cublas_fp32_max_rel_err": err2_f32}
+                           "max_rel_err_full_matrix": m_ours["max_rel"], "cublas_fp32_max_rel_err": m_f32["max_rel"],
+                           "errors_full_matrix": {"fp16_ec": m_ours, "cublas_fp32": m_f32}}
+    tcec.sgemm(a2, b2, c2, policy="tf32_ec")
+    line["square_4096"]["errors_full_matrix"]["tf32_ec"] = error_metrics(torch, c2, exact)
     # ---- the reference's own kernel (test/tcec/batch_gemm.cu:261-386 built for sm_100a) on the same box and
     #      inputs: the checker's library, run here only as a comparator, outside every timed region of this library
     if ref.available():
@@ -524,7 +584,8 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
             torch.cuda.synchronize()
             msr = t0.elapsed_time(t1)  # includes the harness's transposed copy of B (a few percent)
             refgpu[name] = {"tflops": 2.0 * s2 ** 3 / (msr * 1e-3) * 1e-12, "ms": msr,
-                            "max_rel_err_full_matrix": ((cr.double() - exact).abs().max() / scale).item()}
+                            "max_rel_err_full_matrix": ((cr.double() - exact).abs().max() / scale).item(),
+                            "errors_full_matrix": error_metrics(torch, cr, exact)}
         line["reference_gpu"] = refgpu
     del a2, b2, c2, exact
     tcec.device_status()

@@ -124,7 +124,7 @@ def test_options_round_trip():
             tcec.set_option("no_such_option", 1)
         for name, default, other in (("cta_pair", -1, 1), ("path", 0, 2), ("store_turn", 1, 0), ("reserve_sms", 0, 8),
                                      ("static_tiles", 0, 1), ("tile_n", 0, 128), ("comm_sms", 8, 16),
-                                     ("comm_panel_rows", 2048, 512), ("comm_helper", 1, 0)):
+                                     ("comm_panel_rows", 2048, 512), ("comm_helper", 1, 0), ("half_tiles", 1, 0)):
             assert tcec.get_option(name) == default
             tcec.set_option(name, other)
             assert tcec.get_option(name) == other
