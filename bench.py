@@ -709,8 +709,13 @@ def run_sharded(args, torch, np, tcec, sharded, peaks, device, rank, world):
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     e2e_steps = max(2, min(args.steps, 3))
     ms_e = max_over_ranks(torch, time_loop(torch, e2e_step, e2e_steps, True), device, True) / e2e_steps
+    # what the host allows: every rank copies its C block out at the same time and nothing else runs
+    ms_d2h = max_over_ranks(torch, time_loop(torch, lambda: ch.copy_(c, non_blocking=True), 1, True), device, True)
     e2e = {"value": flop / (ms_e * 1e-3) * 1e-12, "unit": UNIT,
            "h2d_bytes_per_step": 4 * (m * k + k * n), "d2h_bytes_per_step": 4 * m * n, "ms_per_step": ms_e,
+           "copy_out_alone_ms": ms_d2h,
+           "copy_out_alone_is": f"all {world} ranks copying their C blocks to pinned host memory at once, nothing else "
+                                f"running: {4.0 * m * n / world / (ms_d2h * 1e-3) * 1e-9:.1f} GB/s per rank",
            "matches_device_resident_result": bool(same.item() == 1.0), "numa_cpus_per_rank": cpus,
            "how": "tcec_sgemm_column_shard_host on every rank: pinned host B block in, C block out, A from pinned host "
                   "memory on rank 0; copy-in, split, broadcast, GEMM and copy-out pipelined in row panels on four streams"}
