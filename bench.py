@@ -436,16 +436,16 @@ def run_single(args, torch, np, tcec, sharded, peaks, device):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 hi/lo products, f32 accumulate",
             "data": "synthetic", "config": bench_config(1, size, tuple(args.large), args.panel_rows),
-            "clocks": clocks, "gpu_launches": 3 * args.steps}  # split A, split B, GEMM
+            "clocks": clocks, "gpu_launches": 2 * args.steps}  # the split of A and B (one launch), the GEMM
     line["config"]["promote_k"] = tcec.get_option("promote_k")
     line["config"]["policy"] = policy
     if args.only == "kernel":
         print(json.dumps(line), flush=True)
         return
 
-    # ---- the dominant kernel inside the step, for the roofline: the step's own three launches (split A,
-    #      split B, GEMM: tcec_pack_a / tcec_pack_b / tcec_sgemm_packed issue exactly what tcec_sgemm does), back
-    #      to back as in the timed region, with an event pair around each GEMM launch
+    # ---- the dominant kernel inside the step, for the roofline: the step's own work (split of A, split of B, GEMM:
+    #      tcec_pack_a / tcec_pack_b / tcec_sgemm_packed run what tcec_sgemm runs, the two splits as two launches
+    #      instead of one), back to back as in the timed region, with an event pair around each GEMM launch
     ap, bp = tcec.pack_a(a, policy), tcec.pack_b(b, policy)
     for _ in range(2):
         tcec.sgemm_packed(ap, bp, m, n, k, c, policy=policy)

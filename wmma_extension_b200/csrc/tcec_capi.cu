@@ -215,9 +215,9 @@ void launch_gemm(const GemmPanelParams& gp, int grid, cudaStream_t stream) {
 
 bool bad_layout(int l) { return l != TCEC_ROW_MAJOR && l != TCEC_COL_MAJOR; }
 
-void pack_operand(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
-                  long long ld, long long stride, int batch, uint8_t* panels, size_t panels_stride,
-                  int policy, cudaStream_t stream, const PackPart& part) {
+static SplitParams split_params(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
+                                long long ld, long long stride, uint8_t* panels, size_t panels_stride, int policy,
+                                const PackPart& part) {
   const int kop = policy_tf32(policy) ? 16 : 32;
   SplitParams sp{};
   sp.src = src;
@@ -235,12 +235,45 @@ void pack_operand(bool k_contiguous, int rows, int k, const float* src, const fl
   sp.elem_stride = part.elem_stride;
   sp.kb_offset = part.kb_offset;
   sp.nkb_out = part.nkb_out;
+  return sp;
+}
+
+void pack_operand(bool k_contiguous, int rows, int k, const float* src, const float* const* src_array,
+                  long long ld, long long stride, int batch, uint8_t* panels, size_t panels_stride,
+                  int policy, cudaStream_t stream, const PackPart& part) {
+  const SplitParams sp = split_params(k_contiguous, rows, k, src, src_array, ld, stride, panels, panels_stride, policy,
+                                      part);
   if (policy_tf32(policy)) {
     if (policy_ec(policy)) launch_split<true, true>(sp, batch, stream);
     else launch_split<true, false>(sp, batch, stream);
   } else {
     if (policy_ec(policy)) launch_split<false, true>(sp, batch, stream);
     else launch_split<false, false>(sp, batch, stream);
+  }
+}
+
+// A (rows = m) and B (rows = n) of one product, in one launch where the grid allows it.
+void pack_both(bool a_k_contiguous, int m, const float* a, const float* const* a_array, long long lda, long long stride_a,
+               uint8_t* panels_a, size_t a_stride, bool b_k_contiguous, int n, const float* b, const float* const* b_array,
+               long long ldb, long long stride_b, uint8_t* panels_b, size_t b_stride, int k, int batch, int policy,
+               cudaStream_t stream) {
+  const PackPart plain;
+  const SplitParams pa = split_params(a_k_contiguous, m, k, a, a_array, lda, stride_a, panels_a, a_stride, policy, plain);
+  const SplitParams pb = split_params(b_k_contiguous, n, k, b, b_array, ldb, stride_b, panels_b, b_stride, policy, plain);
+  const unsigned long long na = static_cast<unsigned long long>(pa.nkb) * pa.row_blocks * batch;
+  const unsigned long long nb = static_cast<unsigned long long>(pb.nkb) * pb.row_blocks * batch;
+  if (na + nb > 0x7fffffffull) {  // beyond one grid: one launch (or several) per operand
+    pack_operand(a_k_contiguous, m, k, a, a_array, lda, stride_a, batch, panels_a, a_stride, policy, stream);
+    pack_operand(b_k_contiguous, n, k, b, b_array, ldb, stride_b, batch, panels_b, b_stride, policy, stream);
+    return;
+  }
+  const unsigned int grid = static_cast<unsigned int>(na + nb), first_b = static_cast<unsigned int>(na);
+  if (policy_tf32(policy)) {
+    if (policy_ec(policy)) tcec_split_both_kernel<true, true><<<grid, 256, 0, stream>>>(pa, pb, first_b);
+    else tcec_split_both_kernel<true, false><<<grid, 256, 0, stream>>>(pa, pb, first_b);
+  } else {
+    if (policy_ec(policy)) tcec_split_both_kernel<false, true><<<grid, 256, 0, stream>>>(pa, pb, first_b);
+    else tcec_split_both_kernel<false, false><<<grid, 256, 0, stream>>>(pa, pb, first_b);
   }
 }
 
@@ -522,10 +555,8 @@ int gemm_impl(int la, int lb, int lc, int m, int n, int k, float alpha, const fl
   if (rel != TCEC_OK) return rel;
   uint8_t* panels_a = static_cast<uint8_t*>(ws);
   uint8_t* panels_b = panels_a + s.a_bytes * batch;
-  pack_operand(la == TCEC_ROW_MAJOR, m, k, a, a_array, lda, stride_a, batch, panels_a, s.a_bytes, policy,
-               stream);
-  pack_operand(lb == TCEC_COL_MAJOR, n, k, b, b_array, ldb, stride_b, batch, panels_b, s.b_bytes, policy,
-               stream);
+  pack_both(la == TCEC_ROW_MAJOR, m, a, a_array, lda, stride_a, panels_a, s.a_bytes, lb == TCEC_COL_MAJOR, n, b, b_array,
+            ldb, stride_b, panels_b, s.b_bytes, k, batch, policy, stream);
   {
     std::lock_guard<std::mutex> lock(g_mu);  // the per-stream tile counters may be created here
     rc = gemm_packed(s, m, n, k, alpha, panels_a, s.a_bytes, panels_b, s.b_bytes, beta, c, c_array, ldc, stride_c,
@@ -1007,8 +1038,8 @@ int tcec_sgemm_static(int layout_a, int layout_b, int layout_c, int m, int n, in
   // status word is only ever raised, never relied on to be clear by the kernels.
   uint8_t* panels_a = sd->panels;
   uint8_t* panels_b = sd->panels + s.a_bytes;  // a_bytes is a multiple of 8192
-  pack_operand(layout_a == TCEC_ROW_MAJOR, m, k, a, nullptr, lda, 0, 1, panels_a, 0, policy, stream);
-  pack_operand(layout_b == TCEC_COL_MAJOR, n, k, b, nullptr, ldb, 0, 1, panels_b, 0, policy, stream);
+  pack_both(layout_a == TCEC_ROW_MAJOR, m, a, nullptr, lda, 0, panels_a, 0, layout_b == TCEC_COL_MAJOR, n, b, nullptr, ldb,
+            0, panels_b, 0, k, 1, policy, stream);
   DeviceState view;  // launch parameters only; owns nothing
   view.status = sd->status;
   view.sm_count = sd->sm_count;
