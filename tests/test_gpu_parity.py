@@ -106,6 +106,29 @@ def test_gemm_matches_oracle(policy, shape):
             assert e_got["max_abs"] < 1e-5  # the reference's unit-test threshold (test/tcec/mma.cu:8)
 
 
+@pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec", "fp16_no_ec"])
+def test_non_finite_and_out_of_range_values_follow_the_reference_semantics(policy):
+    """Values beyond the fp16 range (heads become inf), inf, NaN and subnormals in the operands: every
+    element of C is NaN, +inf, -inf or finite exactly where the CPU restatement says, and the finite
+    ones agree with it (tcec.hpp:219-223: the split itself produces the inf / NaN parts)."""
+    rng = np.random.default_rng(77)
+    m, n, k = 96, 160, 64
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    a[3, 5], a[10, 7], b[9, 2] = 1e5, -7e4, 6.6e4           # beyond fp16: the heads overflow
+    a[20, 1], b[30, 40] = np.inf, np.nan
+    a[40, 3], b[3, 50], a[50, 60] = 1e-30, 3e-41, -2e-39    # tiny and subnormal FP32 values
+    got = _gemm(a, b, policy=policy)
+    want = cpu.tcec_gemm(a, b, policy=policy, rn_block=64 // (16 if policy.startswith("fp16") else 8))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(np.isposinf(got), np.isposinf(want))
+    assert np.array_equal(np.isneginf(got), np.isneginf(want))
+    fin = np.isfinite(want)
+    assert fin.sum() > 0.9 * fin.size and (~fin).sum() > 100
+    tol = 1e-6 if policy.endswith("_ec") else 2e-3
+    assert np.max(np.abs(got[fin] - want[fin])) <= tol * max(1.0, np.max(np.abs(want[fin])))
+
+
 @pytest.mark.parametrize("la", ["row", "col"])
 @pytest.mark.parametrize("lb", ["row", "col"])
 @pytest.mark.parametrize("lc", ["row", "col"])
