@@ -127,6 +127,13 @@ def test_non_finite_and_out_of_range_values_follow_the_reference_semantics(polic
     assert fin.sum() > 0.9 * fin.size and (~fin).sum() > 100
     tol = 1e-6 if policy.endswith("_ec") else 2e-3
     assert np.max(np.abs(got[fin] - want[fin])) <= tol * max(1.0, np.max(np.abs(want[fin])))
+    if policy.startswith("fp16"):
+        # the FP32-tile kernel splits in registers: the same classes, and the same bits where finite
+        tcec.set_option("path", 2)
+        fused = _gemm(a, b, policy=policy)
+        assert np.array_equal(np.isnan(fused), np.isnan(got))
+        assert np.array_equal(np.isposinf(fused), np.isposinf(got)) and np.array_equal(np.isneginf(fused), np.isneginf(got))
+        assert np.array_equal(_bits(fused[fin]), _bits(got[fin]))
 
 
 @pytest.mark.parametrize("la", ["row", "col"])
