@@ -609,6 +609,37 @@ def test_cublas_convention_calls():
                                  0, None) == tcec.ERR_INVALID_ARGUMENT
 
 
+# ---------------------------------------------------------------- CUDA graphs
+@pytest.mark.parametrize("shape,policy", [((512, 768, 256), "fp16_ec"), ((2048, 2304, 512), "tf32_ec"),
+                                          ((300, 200, 100), "fp16_no_ec")])
+def test_calls_can_be_captured_in_a_cuda_graph_and_replayed(shape, policy):
+    """After one call on a stream (which sizes the stream's workspace), tcec_sgemm on that stream is
+    launches only: captured into a CUDA graph and replayed on new operand values it gives the bits of
+    a direct call (the kernels leave their tile counters at zero for the next launch)."""
+    m, n, k = shape
+    rng = np.random.default_rng(2000 + m)
+    a = _t(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = _t(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    c = torch.zeros((m, n), dtype=torch.float32, device=DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        tcec.sgemm(a, b, c, policy=policy)  # sizes the workspace of this stream
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        tcec.sgemm(a, b, c, policy=policy)
+    for rep in range(3):
+        a.copy_(_t(rng.uniform(-1, 1, (m, k)).astype(np.float32)))
+        b.copy_(_t(rng.uniform(-1, 1, (k, n)).astype(np.float32)))
+        c.zero_()
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(c, tcec.sgemm(a, b, policy=policy)), rep
+    tcec.device_status()
+
+
 # ---------------------------------------------------------------- live reference comparator
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref was not built")
 @pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec"])
