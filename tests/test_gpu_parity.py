@@ -640,6 +640,46 @@ def test_calls_can_be_captured_in_a_cuda_graph_and_replayed(shape, policy):
     tcec.device_status()
 
 
+# ---------------------------------------------------------------- host threads
+def test_host_threads_on_their_own_streams_do_not_disturb_each_other():
+    """Four host threads, each with its own stream and shapes, call the library at the same time (ctypes
+    releases the interpreter lock during a call): every result equals the one the same call gives alone.
+    Workspaces and tile counters are per (device, stream); the state mutex only covers their lookup."""
+    import threading
+
+    shapes = [(512, 384, 256, "fp16_ec"), (1300, 700, 96, "tf32_ec"), (256, 2304, 512, "fp16_ec"), (700, 300, 1000, "fp16_no_ec")]
+    rng = np.random.default_rng(4242)
+    work = []
+    for m, n, k, pol in shapes:
+        a = _t(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+        b = _t(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+        work.append((a, b, pol, tcec.sgemm(a, b, policy=pol)))
+    torch.cuda.synchronize()
+    errors = []
+
+    def run(idx):
+        try:
+            a, b, pol, want = work[idx]
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(25):
+                    got = tcec.sgemm(a, b, policy=pol)
+                stream.synchronize()
+                if not torch.equal(got, want):
+                    errors.append(f"thread {idx}: result differs")
+        except Exception as e:  # surfaced below: an exception in a thread would otherwise pass silently
+            errors.append(f"thread {idx}: {e!r}")
+
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(len(work))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not any(t.is_alive() for t in threads)
+    assert not errors, errors
+    tcec.device_status()
+
+
 # ---------------------------------------------------------------- live reference comparator
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref was not built")
 @pytest.mark.parametrize("policy", ["fp16_ec", "tf32_ec"])
