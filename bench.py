@@ -697,7 +697,18 @@ def run_sharded(args, torch, np, tcec, sharded, peaks, device, rank, world):
             "what": "per rank, A already resident and nothing communicated (tcec_sgemm on the rank's block) against the "
                     "sharded step, both timed again back to back in this process: the cost of the split of A on the root, "
                     "the broadcast and the SMs left to it"}
-    del a_all, c_chk
+    # ---- 64 seeded rows and 64 seeded columns of every rank's C block against GPU FP64 products (A is on every
+    #      rank here), in the three error forms; c holds the sharded step's result
+    ri = torch.tensor(sorted({0, m - 1, *np_sample(m, 62, 5100 + rank)}), device=device, dtype=torch.long)
+    ci = torch.tensor(sorted({0, cn - 1, *np_sample(cn, 62, 5200 + rank)}), device=device, dtype=torch.long)
+    ex_r = a_all[ri].double() @ b.double()
+    ex_c = a_all.double() @ b[:, ci].double()
+    er, ec_ = error_metrics(torch, c[ri], ex_r), error_metrics(torch, c[:, ci], ex_c)
+    t = torch.tensor([max(er[q], ec_[q]) for q in ("max_rel", "fro_rel", "max_abs")], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    rows_cols = dict(zip(("max_rel", "fro_rel", "max_abs"), t.tolist()))
+    rows_cols["how"] = "64 seeded rows and 64 seeded columns of every rank's block against GPU FP64 products; maxima over ranks"
+    del a_all, c_chk, ex_r, ex_c
 
     # ---- correctness of every rank's block: sampled rows against the FP64 host loop (outside the timed region)
     rows = [0, 1, m // 2 - 1, m // 2, m - 1]
@@ -709,7 +720,8 @@ def run_sharded(args, torch, np, tcec, sharded, peaks, device, rank, world):
     dmax, rmax, d32, nonfinite = t.tolist()
     accuracy = {"rows_checked_per_rank": len(rows), "ranks_checked": world, "max_rel": dmax / rmax,
                 "fp32_fma_max_rel": d32 / rmax, "nonfinite_fraction": nonfinite,
-                "how": "each rank: sampled rows of its C block against the FP64 host loop; maxima over all ranks"}
+                "how": "each rank: sampled rows of its C block against the FP64 host loop; maxima over all ranks",
+                "rows_and_columns_vs_gpu_fp64": rows_cols}
 
     # ---- end to end at N GPUs: every rank's B block (and A on rank 0) start in pinned host memory on the
     #      rank's NUMA node, every rank's C block ends there; copy-in, broadcast, GEMM and copy-out pipelined
