@@ -116,7 +116,7 @@ int ref_warp_mma(int tf32, int op, int ec, float* d, const float* a, const float
 // Layout fixed by the reference kernel: A row-major (lda >= k), B col-major
 // (ldb >= k), C col-major (ldc >= m).  `per` = CTAs per matrix along m and along n
 // (the reference's BLOCK_M_PER_MATRIX = BLOCK_N_PER_MATRIX): 4 (its own test
-// value, test/tcec/batch_gemm.cu:660), 16 or 32.  Runs on the default stream.
+// value, test/tcec/batch_gemm.cu:660), 16, 32 or 128.  Runs on the default stream.
 int ref_bgemm(int tf32, int per, unsigned m, unsigned n, unsigned k, float alpha, const float* const* a,
               unsigned lda, const float* const* b, unsigned ldb, float beta, float* const* c, unsigned ldc,
               unsigned batch) {
@@ -130,6 +130,7 @@ int ref_bgemm(int tf32, int per, unsigned m, unsigned n, unsigned k, float alpha
     REF_CASE(4)
     REF_CASE(16)
     REF_CASE(32)
+    REF_CASE(128)
     default: return 2;
   }
 #undef REF_CASE
