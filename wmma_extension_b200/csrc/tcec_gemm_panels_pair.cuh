@@ -21,9 +21,10 @@
 //
 // BN = 128 is the same kernel on 256 x 128 half tiles: a half is one 128-row B panel of which each
 // CTA loads its 64 rows (the first or second 4 KB of the panel), multiplied with N = 128, and each
-// epilogue warp holds 64 columns.  The host runs it as a second launch over the tiles of an
-// underfilled last wave, which then lasts half as long; every element of C still sees the same
-// products in the same order.  A launch covers the pair tiles [tile_first, tile_first + tile_count).
+// epilogue warp holds 64 columns.  The host uses it for calls with so few tiles that whole tiles
+// would leave at least half of the SM pairs idle (an N = 128 MMA takes ~0.6 of an N = 256 one, so
+// halving pays only there); every element of C still sees the same products in the same order.
+// A launch covers the pair tiles [tile_first, tile_first + tile_count).
 #pragma once
 #include "sm100_ptx.cuh"
 #include "tcec_gemm_panels.cuh"
