@@ -656,6 +656,38 @@ def test_random_shapes_layouts_and_scalars_agree_across_kernels():
         assert cpu.errors(out[False].cpu().numpy(), want)["max_rel"] < bound, what
 
 
+def test_random_batches_agree_with_single_calls():
+    """Thirty seeded random batches (strided and pointer-array forms, fp16 and tf32, alpha and beta): every
+    matrix of the batch has the bits of a single tcec_sgemm call on it, whichever kernel the batch ran on
+    (FP32 tiles for short K, panels on one SM or on pairs otherwise)."""
+    rng = np.random.default_rng(20261)
+    for case in range(30):
+        batch = int(rng.integers(1, 40))
+        m, n, k = int(rng.integers(1, 420)), int(rng.integers(1, 520)), int(rng.integers(1, 700))
+        if case % 6 == 0:
+            m, n, k = 256, 256, int(rng.choice([64, 256, 512]))
+        policy = ["fp16_ec", "tf32_ec", "fp16_no_ec"][int(rng.integers(0, 3))]
+        alpha = float(rng.choice([1.0, 1.0, 0.5]))
+        beta = float(rng.choice([0.0, 0.0, -1.25]))
+        a = _t(rng.standard_normal((batch, m, k)).astype(np.float32))
+        b = _t(rng.standard_normal((batch, k, n)).astype(np.float32))
+        c0 = _t(rng.standard_normal((batch, m, n)).astype(np.float32))
+        tcec.set_option("path", 1)
+        tcec.set_option("cta_pair", 0)
+        single = torch.stack([tcec.sgemm(a[i], b[i], c0[i].clone(), alpha=alpha, beta=beta, policy=policy)
+                              for i in range(batch)])
+        tcec.set_option("path", 0)
+        tcec.set_option("cta_pair", -1)
+        strided = tcec.sgemm_strided_batched(a, b, c0.clone(), alpha=alpha, beta=beta, policy=policy)
+        cl = [c0[i].clone() for i in range(batch)]
+        tcec.sgemm_batched([a[i] for i in range(batch)], [b[i] for i in range(batch)], cl, alpha=alpha, beta=beta,
+                           policy=policy)
+        tcec.device_status()
+        what = (case, batch, m, n, k, policy, alpha, beta)
+        assert torch.equal(strided, single), what
+        assert torch.equal(torch.stack(cl), single), what
+
+
 # ---------------------------------------------------------------- CUDA graphs
 @pytest.mark.parametrize("shape,policy", [((512, 768, 256), "fp16_ec"), ((2048, 2304, 512), "tf32_ec"),
                                           ((300, 200, 100), "fp16_no_ec")])
